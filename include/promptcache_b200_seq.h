@@ -25,7 +25,15 @@
  *   pcs_moe_rows_*       the chosen experts' gated feed-forward for a handful of rows (weights streamed once)
  *   pcs_moe_plan/_gemm   the same for many rows: rows sorted by expert, grouped tensor-core products
  *   pcs_moe_combine      weighted sum of expert results, pass-through experts and a gated shared expert into the residual
- *   pcs_silu_mul         silu(gate) * up
+ *   pcs_silu_mul         silu(gate) * up;  pcs_glu_mul: the same with the activation as a parameter
+ *   pcs_depth_mix        weighted sum of the results of all earlier layers (depth-weighted average), with the next norm
+ *   pcs_latent_prep      low-rank attention: norms of the query and key/value latents, rotation of the shared key part, append
+ *                        of [latent | rotated part] rows to the slot pool
+ *   pcs_latent_q         rotation of the queries' rotated part; with latent-space queries, their packing beside it
+ *   pcs_latent_expand    per-head key / value rows from up-projected latents and the pool's rotated parts, into a dense pool
+ *   pcs_head_gate        out[t, h, :] = o[t, h, :] * sigmoid(g[t, h])
+ *   pcs_gla_decay        per key channel log decay  logsigmoid(A2 a + b) / tau  of a gated linear-attention layer
+ *   pcs_gla_scan         S_t = diag(alpha_t) S_(t-1) + k_t v_t^T, o_t = S_t^T q_t, per-head output norm and silu gate
  *
  * All tensor arguments are DEVICE pointers; `dtype` selects the compute / storage type of activations, weights and K/V
  * rows: PCS_BF16 or PCS_F32 (true 32-bit everywhere).  The residual stream, norms' statistics, attention scores and
@@ -46,7 +54,7 @@
 extern "C" {
 #endif
 
-#define PCS_ABI_VERSION 2
+#define PCS_ABI_VERSION 3
 #define PCS_BF16 0
 #define PCS_F32 1
 
@@ -64,8 +72,10 @@ int pcs_embed(const void* table, const int64_t* ids, float* out, int n_tokens, i
 int pcs_rmsnorm(const float* x, const int32_t* rows, const void* w, void* out, int n_rows, int width, float eps, int dtype,
                 void* stream);
 
-/* x[r, :] += ls * w * rms(y[r, :] * sigmoid(g[r, :]))   (g may be NULL: no gate; ls may be NULL: no layer scale)
- * then, if next_w != NULL, h_out[r, :] = rms(x[r, :]) * next_w.  y and g are `dtype` with row strides in elements. */
+/* x[r, :] += ls * (w_offset + w) * rms(y[r, :] * sigmoid(g[r, :]))   (g may be NULL: no gate; ls may be NULL: no layer scale)
+ * then, if next_w != NULL, h_out[r, :] = rms(x[r, :]) * (w_offset + next_w).  y and g are `dtype` with row strides in elements
+ * (y is fp32 when y_f32 is set).  w_offset is 0 for plain weights and 1 for weights stored around zero; the sum is formed in
+ * 32-bit. */
 typedef struct pcs_gna_params {
   float* x;
   const void* y;
@@ -78,6 +88,8 @@ typedef struct pcs_gna_params {
   int n_rows, width;
   float eps;
   int dtype;
+  float w_offset;
+  int y_f32;
 } pcs_gna_params;
 int pcs_gate_norm_add(const pcs_gna_params* p, void* stream);
 
@@ -117,7 +129,7 @@ typedef struct pcs_attn_params {
   float scale;
   const float* bias_r1;     /* [H] or NULL: score -= r1[h] * ln(1 + r2[h] * (i - j)) */
   const float* bias_r2;
-  int32_t sink;             /* 1: softmax denominator has one more term exp(0) that carries no value */
+  int32_t sink;             /* 1: the softmax denominator has one more term, exp(sink_logit[h]) (exp(0) without sink_logit), that carries no value */
   const int32_t* tok_seq;
   const int32_t* tok_pos;
   const int32_t* seq_slot;
@@ -132,7 +144,10 @@ typedef struct pcs_attn_params {
   float softcap;            /* > 0: score = softcap * tanh(score / softcap), after the scale and before the bias */
   int32_t window;           /* > 0: query i sees key j only if i - j < window or j < keep_first */
   int32_t keep_first;       /* the first keys of a sequence that stay visible beyond the window */
-  int32_t reserved;
+  int32_t v_row_stride;     /* elements between the value rows of neighbouring keys; 0: vdim.  With a stride the values may be a
+                               leading part of the key rows themselves (v_pool == k_pool, v_row_stride == dim) */
+  const float* sink_logit;  /* [H] or NULL */
+  const int32_t* pool_slot; /* [n_seqs] or NULL: overrides seq_slot (a dense pool that is indexed by the batch entry) */
 } pcs_attn_params;
 /* scratch the key split of pcs_attn needs for n_tokens tokens */
 int64_t pcs_attn_workspace_floats(int n_tokens, int n_heads, int vdim);
@@ -243,16 +258,27 @@ typedef struct pcs_route_params {
   int32_t* idx;             /* [n_tokens, top] */
   float* wgt;               /* [n_tokens, top] */
   float* shared_gate;       /* [n_tokens] or NULL */
-  int32_t dtype, reserved;
+  int32_t dtype;
+  int32_t renorm;           /* 1: wgt is divided by the sum over the token's choices (the softmax over the chosen logits alone) */
+  const float* bias;        /* [n_outputs] or NULL: added to z before the softmax */
 } pcs_route_params;
 int pcs_moe_route(const pcs_route_params* p, void* stream);
+
+/* The gated activation of a feed-forward: PCS_GLU_SILU  silu(g) * u;   PCS_GLU_CLAMPED_SWISH  g' = min(g, limit),
+ * u' = clamp(u, -limit, limit), g' * sigmoid(alpha * g') * (u' + 1).  A NULL pointer means PCS_GLU_SILU. */
+#define PCS_GLU_SILU 0
+#define PCS_GLU_CLAMPED_SWISH 1
+typedef struct pcs_glu_act {
+  int32_t kind;
+  float alpha, limit;
+} pcs_glu_act;
 
 /* The chosen experts for a handful of rows.  Pair p = (token p / top, choice p % top), expert e = idx[p]; e >= n_experts is a
  * pass-through output and is skipped.  w_gu [n_experts, 2*ff, width] (gate rows, then up rows), w_down [n_experts, width, ff].
  *   pcs_moe_rows_up:    act[p, :] = silu(W_gate_e h) * (W_up_e h)        act `dtype` [pairs, ff]
  *   pcs_moe_rows_down:  y[p, :]  = W_down_e act[p, :]                    y fp32 [pairs, width] */
 int pcs_moe_rows_up(const void* h, int64_t h_stride, const void* w_gu, const int32_t* idx, void* act, int n_pairs, int top, int n_experts,
-                    int ff, int width, int dtype, void* stream);
+                    int ff, int width, const pcs_glu_act* glu, int dtype, void* stream);
 int pcs_moe_rows_down(const void* act, const void* w_down, const int32_t* idx, float* y, int n_pairs, int n_experts, int ff, int width,
                       int dtype, void* stream);
 
@@ -270,7 +296,7 @@ int pcs_moe_gather(const void* h, int64_t h_stride, const int32_t* plan, void* o
  * stage 1: y[pair, :] = W_down_e act[sorted row, :]                                      (fp32 [n_pairs, width])
  * bfloat16 only; ff and width multiples of 8. */
 int pcs_moe_gemm(int stage, const void* a, int64_t a_stride, const void* w, const int32_t* plan, void* out, int n_pairs, int top,
-                 int n_experts, int ff, int width, void* stream);
+                 int n_experts, int ff, int width, const pcs_glu_act* glu, void* stream);
 
 /* x[t] += mult * ( sum_k wgt[t,k] * (idx[t,k] < n_experts ? y[row(t*top + k)] : h[t]) + (ys ? shared_gate[t] * ys[t] : 0) )
  * row(p) = y_row ? y_row[p] : p;  y is fp32 (y_dtype PCS_F32) or `dtype`. */
@@ -292,6 +318,123 @@ int pcs_moe_combine(const pcs_combine_params* p, void* stream);
 
 /* out[r, c] = silu(gu[r, c]) * gu[r, ff + c]     (gu `dtype` [n_rows, gu_stride], out `dtype` [n_rows, ff]) */
 int pcs_silu_mul(const void* gu, int64_t gu_stride, void* out, int n_rows, int ff, int dtype, void* stream);
+/* out[r, c] = glu(gu[r, c], gu[r, ff + c]) */
+int pcs_glu_mul(const void* gu, int64_t gu_stride, void* out, int n_rows, int ff, const pcs_glu_act* glu, int dtype, void* stream);
+
+/* Depth-weighted average: out[r, :] = sum_{j < n_terms} coef[j] * xs[j][row(r), :], row(r) = rows ? rows[r] : r, where xs[j] is the
+ * fp32 matrix at xs + j * term_stride elements.  x_out (fp32 [n_rows, width]) may be NULL; when next_w is given,
+ * h_out[r, :] = rms(out[r, :]) * (w_offset + next_w)  (`dtype`).  The sum runs over j in increasing order. */
+typedef struct pcs_depthmix_params {
+  const float* xs;
+  int64_t term_stride;
+  int32_t n_terms;
+  const float* coef;        /* [n_terms] */
+  const int32_t* rows;      /* [n_rows] or NULL */
+  float* x_out;
+  const void* next_w;       /* [width] `dtype` or NULL */
+  void* h_out;              /* [n_rows, width] `dtype` */
+  float w_offset, eps;
+  int32_t n_rows, width, dtype, reserved;
+} pcs_depthmix_params;
+int pcs_depth_mix(const pcs_depthmix_params* p, void* stream);
+
+/* Low-rank (latent) attention.  `proj` holds per token the query latent (q_rank numbers at cq_off) and the key/value latent
+ * followed by the key part that is rotated (kv_rank + rot_dim numbers at ckv_off).
+ *   cq_out[t]                       = rms(query latent) * cq_norm_w                              [n_tokens, q_rank]
+ *   pool[slot, pos, 0:kv_rank]      = rms(key/value latent) * ckv_norm_w
+ *   pool[slot, pos, kv_rank: ...]   = the rotated part turned by pos (pairs (i, i + rot_dim/2), cos and sin times rot_mult)
+ * pool is [slots, cap, kv_rank + rot_dim]. */
+typedef struct pcs_latent_prep_params {
+  const void* proj;
+  int64_t row_stride;
+  int32_t cq_off, ckv_off, q_rank, kv_rank, rot_dim;
+  const void* cq_norm_w;    /* [q_rank] */
+  const void* ckv_norm_w;   /* [kv_rank] */
+  float eps;
+  const double* freqs;      /* [rot_dim / 2] */
+  float rot_mult;
+  void* cq_out;
+  void* pool;
+  int32_t cap;
+  const int32_t* tok_seq;
+  const int32_t* tok_pos;
+  const int32_t* seq_slot;
+  int32_t n_tokens, dtype;
+} pcs_latent_prep_params;
+int pcs_latent_prep(const pcs_latent_prep_params* p, void* stream);
+
+/* Queries of latent attention.  q [n_tokens, H * (dim + rot_dim)], per head [dim plain | rot_dim rotated].
+ *   q_lat == NULL:  the rotated part of every head is turned by the token's position in place (q_out == q) or into q_out
+ *                   (same layout, plain part copied).
+ *   q_lat != NULL:  q_out [n_tokens, H * (kv_rank + rot_dim)] gets per head [q_lat[t, h, :] | rotated part], where
+ *                   q_lat[t, h, c] sits at q_lat + t * lat_tok_stride + h * lat_head_stride + c. */
+typedef struct pcs_latent_q_params {
+  const void* q;
+  void* q_out;
+  const void* q_lat;
+  int64_t lat_tok_stride, lat_head_stride;
+  int32_t n_heads, dim, rot_dim, kv_rank;
+  const double* freqs;
+  float rot_mult;
+  const int32_t* tok_pos;
+  int32_t n_tokens, dtype;
+} pcs_latent_q_params;
+int pcs_latent_q(const pcs_latent_q_params* p, void* stream);
+
+/* Per-head rows for attention over expanded keys and values.  kv [n_ctx, H * (dim + vdim)]: for context token n (entry
+ * ctx_seq[n], position ctx_pos[n]) the plain key parts of all heads, then the values of all heads.
+ *   k_dense[b, h, pos, :] = [kv[n, h * dim ...] | pool[seq_slot[b], pos, kv_rank : kv_rank + rot_dim]]     [B, H, cap_dense, dim + rot_dim]
+ *   v_dense[b, h, pos, :] = kv[n, H * dim + h * vdim ...]                                                   [B, H, cap_dense, vdim] */
+typedef struct pcs_latent_expand_params {
+  const void* kv;
+  int64_t kv_stride;
+  const void* pool;
+  int32_t cap, kv_rank, rot_dim, n_heads, dim, vdim;
+  void* k_dense;
+  void* v_dense;
+  int32_t cap_dense;
+  const int32_t* ctx_seq;
+  const int32_t* ctx_pos;
+  const int32_t* seq_slot;
+  int32_t n_ctx, dtype;
+} pcs_latent_expand_params;
+int pcs_latent_expand(const pcs_latent_expand_params* p, void* stream);
+
+/* rows of the latent pool (the first `width` numbers of each) for the context tokens, as one matrix: out[n, :] = pool[seq_slot[ctx_seq[n]], ctx_pos[n], 0:width] */
+int pcs_latent_gather(const void* pool, int cap, int row_width, int width, void* out, const int32_t* ctx_seq, const int32_t* ctx_pos,
+                      const int32_t* seq_slot, int n_ctx, int dtype, void* stream);
+
+/* out[t, h * vdim + c] = o[t * o_tok_stride + h * o_head_stride + c] * sigmoid(g[t * g_stride + h])       (out contiguous) */
+int pcs_head_gate(const void* o, int64_t o_tok_stride, int64_t o_head_stride, const void* g, int64_t g_stride, void* out, int n_tokens,
+                  int n_heads, int vdim, int dtype, void* stream);
+
+/* Gated linear attention.  log decay per key channel: ld[t, c] = logsigmoid(sum_r a2[c, r] * a[t, r] + a2_b[c]) / tau   (fp32
+ * [n_tokens, n_channels]); `a` is `dtype` [n_tokens, a_stride] with `rank` numbers per token, a2 `dtype` [n_channels, rank]. */
+int pcs_gla_decay(const void* a, int64_t a_stride, const void* a2, const float* a2_b, float* ld, int n_tokens, int n_channels, int rank,
+                  float tau, int dtype, void* stream);
+
+/* Per entry and head, token by token:  S <- diag(exp(ld_t)) S + k_t v_t^T,  o_t = S^T (q_t * q_scale);  then
+ * out[t, h, :] = o_t / sqrt(mean(o_t^2) + eps) * norm_w * silu(g[t, h, :])   (norm_w [vdim], shared by the heads).
+ * S is fp32 [slots, heads, dim, vdim] in the slot pool; an entry whose slot holds no tokens starts from zero. */
+typedef struct pcs_gla_params {
+  const void* proj;         /* [n_tokens, row_stride]: q at q_off, k at k_off, v at v_off, the gate's pre-activation at g_off */
+  int64_t row_stride;
+  int32_t q_off, k_off, v_off, g_off;
+  const float* ld;          /* [n_tokens, heads * dim] log decays */
+  const void* norm_w;       /* [vdim] `dtype` */
+  void* out;                /* [n_tokens, heads * vdim] `dtype` */
+  float* s_pool;
+  int32_t heads, dim, vdim;
+  float q_scale, eps;
+  const int32_t* seq_slot;
+  const int32_t* seq_pos0;
+  const int32_t* seq_len;
+  const int32_t* seq_off;
+  int32_t n_seqs, n_tokens, dtype, max_len;
+  int32_t impl;             /* 0 = automatic, 1 = the kernel with the state in shared memory */
+  float* o_raw;             /* fp32 scratch [n_tokens, heads * vdim] */
+} pcs_gla_params;
+int pcs_gla_scan(const pcs_gla_params* p, void* stream);
 
 #ifdef __cplusplus
 }

@@ -18,13 +18,16 @@ LIB_PATH = os.path.join(_HERE, "libpromptcache_b200_seq.so")
 PCS_BF16, PCS_F32 = 0, 1
 EXPORTS = ("pcs_version", "pcs_last_error", "pcs_launch_count", "pcs_attn_workspace_floats", "pcs_embed", "pcs_rmsnorm", "pcs_gate_norm_add", "pcs_xielu", "pcs_linear_rows",
            "pcs_qk_prep", "pcs_attn", "pcs_mlstm_gates", "pcs_mlstm_scan", "pcs_embed_bigram", "pcs_norm_conv", "pcs_rope_kv_prep", "pcs_moe_route",
-           "pcs_moe_rows_up", "pcs_moe_rows_down", "pcs_moe_plan", "pcs_moe_gather", "pcs_moe_gemm", "pcs_moe_combine", "pcs_silu_mul")
+           "pcs_moe_rows_up", "pcs_moe_rows_down", "pcs_moe_plan", "pcs_moe_gather", "pcs_moe_gemm", "pcs_moe_combine", "pcs_silu_mul", "pcs_glu_mul",
+           "pcs_depth_mix", "pcs_latent_prep", "pcs_latent_q", "pcs_latent_gather", "pcs_latent_expand", "pcs_head_gate", "pcs_gla_decay", "pcs_gla_scan")
+GLU_SILU, GLU_CLAMPED_SWISH = 0, 1
 
 
 class pcs_gna_params(C.Structure):
     _fields_ = [("x", C.c_void_p), ("y", C.c_void_p), ("g", C.c_void_p), ("y_stride", C.c_int64), ("g_stride", C.c_int64),
                 ("w", C.c_void_p), ("ls", C.c_void_p), ("next_w", C.c_void_p), ("h_out", C.c_void_p),
-                ("n_rows", C.c_int32), ("width", C.c_int32), ("eps", C.c_float), ("dtype", C.c_int32)]
+                ("n_rows", C.c_int32), ("width", C.c_int32), ("eps", C.c_float), ("dtype", C.c_int32),
+                ("w_offset", C.c_float), ("y_f32", C.c_int32)]
 
 
 class pcs_qkprep_params(C.Structure):
@@ -46,7 +49,8 @@ class pcs_attn_params(C.Structure):
                 ("seq_len", C.c_void_p), ("seq_off", C.c_void_p),
                 ("n_tokens", C.c_int32), ("n_seqs", C.c_int32), ("max_len", C.c_int32), ("dtype", C.c_int32),
                 ("impl", C.c_int32), ("max_keys", C.c_int32), ("workspace", C.c_void_p), ("workspace_floats", C.c_int64),
-                ("softcap", C.c_float), ("window", C.c_int32), ("keep_first", C.c_int32), ("reserved", C.c_int32)]
+                ("softcap", C.c_float), ("window", C.c_int32), ("keep_first", C.c_int32), ("v_row_stride", C.c_int32),
+                ("sink_logit", C.c_void_p), ("pool_slot", C.c_void_p)]
 
 
 class pcs_normconv_params(C.Structure):
@@ -68,7 +72,45 @@ class pcs_route_params(C.Structure):
     _fields_ = [("h", C.c_void_p), ("h_stride", C.c_int64), ("w_router", C.c_void_p), ("correction", C.c_void_p), ("w_sg", C.c_void_p),
                 ("n_tokens", C.c_int32), ("width", C.c_int32), ("n_outputs", C.c_int32), ("top", C.c_int32), ("n_groups", C.c_int32),
                 ("keep_groups", C.c_int32), ("idx", C.c_void_p), ("wgt", C.c_void_p), ("shared_gate", C.c_void_p),
-                ("dtype", C.c_int32), ("reserved", C.c_int32)]
+                ("dtype", C.c_int32), ("renorm", C.c_int32), ("bias", C.c_void_p)]
+
+
+class pcs_glu_act(C.Structure):
+    _fields_ = [("kind", C.c_int32), ("alpha", C.c_float), ("limit", C.c_float)]
+
+
+class pcs_depthmix_params(C.Structure):
+    _fields_ = [("xs", C.c_void_p), ("term_stride", C.c_int64), ("n_terms", C.c_int32), ("coef", C.c_void_p), ("rows", C.c_void_p),
+                ("x_out", C.c_void_p), ("next_w", C.c_void_p), ("h_out", C.c_void_p), ("w_offset", C.c_float), ("eps", C.c_float),
+                ("n_rows", C.c_int32), ("width", C.c_int32), ("dtype", C.c_int32), ("reserved", C.c_int32)]
+
+
+class pcs_latent_prep_params(C.Structure):
+    _fields_ = [("proj", C.c_void_p), ("row_stride", C.c_int64), ("cq_off", C.c_int32), ("ckv_off", C.c_int32), ("q_rank", C.c_int32),
+                ("kv_rank", C.c_int32), ("rot_dim", C.c_int32), ("cq_norm_w", C.c_void_p), ("ckv_norm_w", C.c_void_p), ("eps", C.c_float),
+                ("freqs", C.c_void_p), ("rot_mult", C.c_float), ("cq_out", C.c_void_p), ("pool", C.c_void_p), ("cap", C.c_int32),
+                ("tok_seq", C.c_void_p), ("tok_pos", C.c_void_p), ("seq_slot", C.c_void_p), ("n_tokens", C.c_int32), ("dtype", C.c_int32)]
+
+
+class pcs_latent_q_params(C.Structure):
+    _fields_ = [("q", C.c_void_p), ("q_out", C.c_void_p), ("q_lat", C.c_void_p), ("lat_tok_stride", C.c_int64), ("lat_head_stride", C.c_int64),
+                ("n_heads", C.c_int32), ("dim", C.c_int32), ("rot_dim", C.c_int32), ("kv_rank", C.c_int32), ("freqs", C.c_void_p),
+                ("rot_mult", C.c_float), ("tok_pos", C.c_void_p), ("n_tokens", C.c_int32), ("dtype", C.c_int32)]
+
+
+class pcs_latent_expand_params(C.Structure):
+    _fields_ = [("kv", C.c_void_p), ("kv_stride", C.c_int64), ("pool", C.c_void_p), ("cap", C.c_int32), ("kv_rank", C.c_int32),
+                ("rot_dim", C.c_int32), ("n_heads", C.c_int32), ("dim", C.c_int32), ("vdim", C.c_int32), ("k_dense", C.c_void_p),
+                ("v_dense", C.c_void_p), ("cap_dense", C.c_int32), ("ctx_seq", C.c_void_p), ("ctx_pos", C.c_void_p), ("seq_slot", C.c_void_p),
+                ("n_ctx", C.c_int32), ("dtype", C.c_int32)]
+
+
+class pcs_gla_params(C.Structure):
+    _fields_ = [("proj", C.c_void_p), ("row_stride", C.c_int64), ("q_off", C.c_int32), ("k_off", C.c_int32), ("v_off", C.c_int32), ("g_off", C.c_int32),
+                ("ld", C.c_void_p), ("norm_w", C.c_void_p), ("out", C.c_void_p), ("s_pool", C.c_void_p),
+                ("heads", C.c_int32), ("dim", C.c_int32), ("vdim", C.c_int32), ("q_scale", C.c_float), ("eps", C.c_float),
+                ("seq_slot", C.c_void_p), ("seq_pos0", C.c_void_p), ("seq_len", C.c_void_p), ("seq_off", C.c_void_p),
+                ("n_seqs", C.c_int32), ("n_tokens", C.c_int32), ("dtype", C.c_int32), ("max_len", C.c_int32), ("impl", C.c_int32), ("o_raw", C.c_void_p)]
 
 
 class pcs_combine_params(C.Structure):
@@ -125,8 +167,8 @@ def load() -> C.CDLL:
     lib.pcs_norm_conv.argtypes = [C.POINTER(pcs_normconv_params), C.c_void_p]
     lib.pcs_rope_kv_prep.argtypes = [C.POINTER(pcs_rope_params), C.c_void_p]
     lib.pcs_moe_route.argtypes = [C.POINTER(pcs_route_params), C.c_void_p]
-    lib.pcs_moe_rows_up.argtypes = [C.c_void_p, C.c_int64, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int,
-                                    C.c_void_p]
+    lib.pcs_moe_rows_up.argtypes = [C.c_void_p, C.c_int64, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int,
+                                    C.c_void_p, C.c_int, C.c_void_p]
     lib.pcs_moe_rows_down.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_void_p]
     # (the grouped products are declared below)
     lib.pcs_moe_plan_ints.argtypes = [C.c_int, C.c_int]
@@ -136,9 +178,18 @@ def load() -> C.CDLL:
     lib.pcs_moe_plan_part.restype = C.c_int
     lib.pcs_moe_gather.argtypes = [C.c_void_p, C.c_int64, C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_int, C.c_void_p]
     lib.pcs_moe_gemm.argtypes = [C.c_int, C.c_void_p, C.c_int64, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int,
-                                 C.c_void_p]
+                                 C.c_void_p, C.c_void_p]
     lib.pcs_moe_combine.argtypes = [C.POINTER(pcs_combine_params), C.c_void_p]
     lib.pcs_silu_mul.argtypes = [C.c_void_p, C.c_int64, C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_void_p]
+    lib.pcs_glu_mul.argtypes = [C.c_void_p, C.c_int64, C.c_void_p, C.c_int, C.c_int, C.c_void_p, C.c_int, C.c_void_p]
+    lib.pcs_depth_mix.argtypes = [C.POINTER(pcs_depthmix_params), C.c_void_p]
+    lib.pcs_latent_prep.argtypes = [C.POINTER(pcs_latent_prep_params), C.c_void_p]
+    lib.pcs_latent_q.argtypes = [C.POINTER(pcs_latent_q_params), C.c_void_p]
+    lib.pcs_latent_gather.argtypes = [C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_void_p]
+    lib.pcs_latent_expand.argtypes = [C.POINTER(pcs_latent_expand_params), C.c_void_p]
+    lib.pcs_head_gate.argtypes = [C.c_void_p, C.c_int64, C.c_int64, C.c_void_p, C.c_int64, C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_int, C.c_void_p]
+    lib.pcs_gla_decay.argtypes = [C.c_void_p, C.c_int64, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_float, C.c_int, C.c_void_p]
+    lib.pcs_gla_scan.argtypes = [C.POINTER(pcs_gla_params), C.c_void_p]
     for name in EXPORTS[4:]:
         getattr(lib, name).restype = C.c_int
     _lib = lib
@@ -226,10 +277,11 @@ def rmsnorm(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, eps: float, row
 
 
 def gate_norm_add(x: torch.Tensor, y: torch.Tensor, g: Optional[torch.Tensor], w: torch.Tensor, ls: Optional[torch.Tensor], eps: float,
-                  next_w: Optional[torch.Tensor] = None, h_out: Optional[torch.Tensor] = None) -> None:
-    """x += ls * w * rms_norm(y * sigmoid(g)); then h_out = rms_norm(x) * next_w when next_w is given."""
+                  next_w: Optional[torch.Tensor] = None, h_out: Optional[torch.Tensor] = None, w_offset: float = 0.0) -> None:
+    """x += ls * (w_offset + w) * rms_norm(y * sigmoid(g)); then h_out = rms_norm(x) * (w_offset + next_w) when next_w is given.  y is
+    in the weights' type or float32."""
     _cuda(x, y, g, w, ls, next_w, h_out)
-    _rows2d(y, w.dtype, "gate_norm_add: y")
+    _rows2d(y, torch.float32 if y.dtype == torch.float32 else w.dtype, "gate_norm_add: y")
     if g is not None:
         _rows2d(g, w.dtype, "gate_norm_add: g")
     if x.dtype != torch.float32 or not x.is_contiguous() or x.shape != y.shape:
@@ -240,6 +292,7 @@ def gate_norm_add(x: torch.Tensor, y: torch.Tensor, g: Optional[torch.Tensor], w
     p.x, p.y, p.g, p.y_stride, p.g_stride = x.data_ptr(), y.data_ptr(), _ptr(g), y.stride(0), g.stride(0) if g is not None else 0
     p.w, p.ls, p.next_w, p.h_out = w.data_ptr(), _ptr(ls), _ptr(next_w), _ptr(h_out)
     p.n_rows, p.width, p.eps, p.dtype = x.shape[0], x.shape[1], float(eps), dtype_code(w.dtype)
+    p.w_offset, p.y_f32 = float(w_offset), 1 if (y.dtype == torch.float32 and w.dtype != torch.float32) else 0
     _check(load().pcs_gate_norm_add(C.byref(p), _stream()), "pcs_gate_norm_add")
 
 
@@ -304,12 +357,20 @@ def qk_prep(qkv: torch.Tensor, offs, q_norm_w, k_norm_w, eps: float, n_heads: in
 def attention(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor, out: torch.Tensor, n_heads: int, scale: float,
               r1: Optional[torch.Tensor], r2: Optional[torch.Tensor], sink: bool, batch: Batch, impl: int = 0,
               max_keys: int = 0, workspace: Optional[torch.Tensor] = None, softcap: float = 0.0, window: int = 0,
-              keep_first: int = 0) -> None:
+              keep_first: int = 0, sink_logit: Optional[torch.Tensor] = None, v_row_stride: int = 0,
+              pool_slot: Optional[torch.Tensor] = None) -> None:
     """q [T, H*dim], out [T, H*vdim]; causal over each entry's own slot rows; r1 / r2 float32 [H] or None.  With a float32
     `workspace` (attn_workspace) and `max_keys` (upper bound of the keys a token sees) few tokens over many keys are run
     as several splits of the keys that a second launch merges.  `softcap` > 0 caps the scaled score by softcap * tanh(s /
-    softcap); `window` > 0 limits query i to keys j with i - j < window or j < keep_first."""
-    _cuda(q, k_pool, v_pool, out, r1, r2)
+    softcap); `window` > 0 limits query i to keys j with i - j < window or j < keep_first.  `sink_logit` (float32 [H], with
+    sink=True): the sink's term is exp(sink_logit[h]) instead of exp(0).  `v_row_stride` > 0: a key's value row starts that many
+    elements after the previous key's (the values may be a leading part of the key rows: pass the key pool as v_pool too; vdim is
+    then out's width per head).  `pool_slot` (int32 [entries]) replaces the batch's slots."""
+    _cuda(q, k_pool, v_pool, out, r1, r2, sink_logit, pool_slot)
+    if sink_logit is not None and (sink_logit.dtype != torch.float32 or sink_logit.numel() != n_heads or not sink_logit.is_contiguous()):
+        raise NativeError("attention: sink_logit must be float32 [H]")
+    if pool_slot is not None and (pool_slot.dtype != torch.int32 or pool_slot.numel() != batch.n_seqs or not pool_slot.is_contiguous()):
+        raise NativeError("attention: pool_slot must be int32 [entries]")
     dt = q.dtype
     if not (q.is_contiguous() and out.is_contiguous() and k_pool.is_contiguous() and v_pool.is_contiguous()) or out.dtype != dt \
             or k_pool.dtype != dt or v_pool.dtype != dt:
@@ -319,7 +380,9 @@ def attention(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor, out: 
             raise NativeError("attention: the distance-bias numbers must be float32 [H]")
     p = pcs_attn_params()
     p.q, p.k_pool, p.v_pool, p.out = q.data_ptr(), k_pool.data_ptr(), v_pool.data_ptr(), out.data_ptr()
-    p.n_heads, p.n_kv_heads, p.dim, p.vdim, p.cap = n_heads, k_pool.shape[1], k_pool.shape[3], v_pool.shape[3], k_pool.shape[2]
+    p.n_heads, p.n_kv_heads, p.dim, p.cap = n_heads, k_pool.shape[1], k_pool.shape[3], k_pool.shape[2]
+    p.vdim = out.shape[1] // n_heads if v_row_stride else v_pool.shape[3]
+    p.v_row_stride, p.sink_logit, p.pool_slot = int(v_row_stride), _ptr(sink_logit), _ptr(pool_slot)
     p.scale, p.bias_r1, p.bias_r2, p.sink = float(scale), _ptr(r1), _ptr(r2), 1 if sink else 0
     p.tok_seq, p.tok_pos, p.seq_slot = batch.tok_seq.data_ptr(), batch.tok_pos.data_ptr(), batch.seq_slot.data_ptr()
     p.seq_pos0, p.seq_len, p.seq_off = batch.seq_pos0.data_ptr(), batch.seq_len.data_ptr(), batch.seq_off.data_ptr()
@@ -448,10 +511,13 @@ def rope_kv_prep(qkv: torch.Tensor, offs, n_heads: int, n_kv_heads: int, dim: in
     _check(load().pcs_rope_kv_prep(C.byref(p), _stream()), "pcs_rope_kv_prep")
 
 
-def moe_route(h: torch.Tensor, w_router: torch.Tensor, correction: Optional[torch.Tensor], w_sg: Optional[torch.Tensor], top: int, n_groups: int,
-              keep_groups: int):
-    """(idx int32 [T, top], wgt float32 [T, top], shared gate float32 [T] or None)."""
-    _cuda(h, w_router, correction, w_sg)
+def moe_route(h: torch.Tensor, w_router: torch.Tensor, correction: Optional[torch.Tensor], w_sg: Optional[torch.Tensor], top: int, n_groups: int = 1,
+              keep_groups: int = 1, bias: Optional[torch.Tensor] = None, renorm: bool = False):
+    """(idx int32 [T, top], wgt float32 [T, top], shared gate float32 [T] or None).  `bias` (float32 [outputs]) is added to the
+    router's outputs; `renorm`: the weights are the softmax over the chosen outputs alone."""
+    _cuda(h, w_router, correction, w_sg, bias)
+    if bias is not None and (bias.dtype != torch.float32 or not bias.is_contiguous() or bias.numel() != w_router.shape[0]):
+        raise NativeError("moe_route: bias must be float32 [outputs]")
     dt = h.dtype
     _rows2d(h, dt, "moe_route: h")
     if w_router.dtype != dt or not w_router.is_contiguous() or w_router.shape[1] != h.shape[1]:
@@ -468,6 +534,7 @@ def moe_route(h: torch.Tensor, w_router: torch.Tensor, correction: Optional[torc
     p.h, p.h_stride, p.w_router, p.correction, p.w_sg = h.data_ptr(), h.stride(0), w_router.data_ptr(), _ptr(correction), _ptr(w_sg)
     p.n_tokens, p.width, p.n_outputs, p.top, p.n_groups, p.keep_groups = T, h.shape[1], w_router.shape[0], int(top), int(n_groups), int(keep_groups)
     p.idx, p.wgt, p.shared_gate, p.dtype = idx.data_ptr(), wgt.data_ptr(), _ptr(sg), dtype_code(dt)
+    p.renorm, p.bias = 1 if renorm else 0, _ptr(bias)
     _check(load().pcs_moe_route(C.byref(p), _stream()), "pcs_moe_route")
     return idx, wgt, sg
 
@@ -475,7 +542,15 @@ def moe_route(h: torch.Tensor, w_router: torch.Tensor, correction: Optional[torc
 MOE_ROWS_MAX_PAIRS = 64
 
 
-def moe_experts(h: torch.Tensor, idx: torch.Tensor, w_gu: torch.Tensor, w_down: torch.Tensor, grouped=None):
+def _glu(act):
+    """None (silu(g) * u) or (kind, alpha, limit) -> the C struct (pass C.byref of it; None stays None)."""
+    if act is None:
+        return None
+    kind, alpha, limit = act
+    return C.byref(pcs_glu_act(int(kind), float(alpha), float(limit)))
+
+
+def moe_experts(h: torch.Tensor, idx: torch.Tensor, w_gu: torch.Tensor, w_down: torch.Tensor, grouped=None, act=None):
     """The chosen experts' results: (y [rows, width], row_of) where pair p = (token p // top, choice p % top) finds its result
     in row row_of[p] of y (row_of None: row p); rows of pass-through choices are not written.  w_gu [E, 2 ff, width] (gate rows,
     then up rows), w_down [E, width, ff].
@@ -485,7 +560,8 @@ def moe_experts(h: torch.Tensor, idx: torch.Tensor, w_gu: torch.Tensor, w_down: 
                           in the sorted order
       grouped="own"       the same through this library's grouped tensor-core kernel (`pcs_moe_gemm`), activation in its
                           epilogue, y float32 by pair
-    None chooses by size: the row kernels up to 64 pairs, otherwise the library's product (or this library's where torch has none)."""
+    None chooses by size: the row kernels up to 64 pairs, otherwise the library's product (or this library's where torch has none).
+    `act`: None for silu(gate) * up, or (kind, alpha, limit) of the gated activation (GLU_CLAMPED_SWISH)."""
     _cuda(h, idx, w_gu, w_down)
     dt = h.dtype
     _rows2d(h, dt, "moe_experts: h")
@@ -512,9 +588,9 @@ def moe_experts(h: torch.Tensor, idx: torch.Tensor, w_gu: torch.Tensor, w_down: 
         _check(lib.pcs_moe_plan(idx.data_ptr(), P, E, plan.data_ptr(), _stream()), "pcs_moe_plan")
         if grouped == "own":
             y = torch.empty(P, W, dtype=torch.float32, device=h.device)
-            act = torch.empty(P, ff, dtype=dt, device=h.device)
-            _check(lib.pcs_moe_gemm(0, h.data_ptr(), h.stride(0), w_gu.data_ptr(), plan.data_ptr(), act.data_ptr(), P, top, E, ff, W, _stream()), "pcs_moe_gemm")
-            _check(lib.pcs_moe_gemm(1, act.data_ptr(), ff, w_down.data_ptr(), plan.data_ptr(), y.data_ptr(), P, top, E, ff, W, _stream()), "pcs_moe_gemm")
+            a_buf = torch.empty(P, ff, dtype=dt, device=h.device)
+            _check(lib.pcs_moe_gemm(0, h.data_ptr(), h.stride(0), w_gu.data_ptr(), plan.data_ptr(), a_buf.data_ptr(), P, top, E, ff, W, _glu(act), _stream()), "pcs_moe_gemm")
+            _check(lib.pcs_moe_gemm(1, a_buf.data_ptr(), ff, w_down.data_ptr(), plan.data_ptr(), y.data_ptr(), P, top, E, ff, W, None, _stream()), "pcs_moe_gemm")
             return y, None
         if grouped != "library" or not has_library:
             raise NativeError(f"moe_experts: unknown grouped mode {grouped!r} (or torch has no grouped product)")
@@ -523,13 +599,13 @@ def moe_experts(h: torch.Tensor, idx: torch.Tensor, w_gu: torch.Tensor, w_down: 
         a = torch.empty(P, W, dtype=dt, device=h.device)
         _check(lib.pcs_moe_gather(h.data_ptr(), h.stride(0), plan.data_ptr(), a.data_ptr(), P, top, E, W, _stream()), "pcs_moe_gather")
         gu = torch.nn.functional.grouped_mm(a, w_gu.transpose(1, 2), offs=ends)
-        y = torch.nn.functional.grouped_mm(silu_mul(gu, ff), w_down.transpose(1, 2), offs=ends)
+        y = torch.nn.functional.grouped_mm(glu_mul(gu, ff, act), w_down.transpose(1, 2), offs=ends)
         return y, row_of
     y = torch.empty(P, W, dtype=torch.float32, device=h.device)
-    act = torch.empty(P, ff, dtype=dt, device=h.device)
-    _check(load().pcs_moe_rows_up(h.data_ptr(), h.stride(0), w_gu.data_ptr(), idx.data_ptr(), act.data_ptr(), P, top, E, ff, W, dtype_code(dt), _stream()),
-           "pcs_moe_rows_up")
-    _check(load().pcs_moe_rows_down(act.data_ptr(), w_down.data_ptr(), idx.data_ptr(), y.data_ptr(), P, E, ff, W, dtype_code(dt), _stream()),
+    a_buf = torch.empty(P, ff, dtype=dt, device=h.device)
+    _check(load().pcs_moe_rows_up(h.data_ptr(), h.stride(0), w_gu.data_ptr(), idx.data_ptr(), a_buf.data_ptr(), P, top, E, ff, W, _glu(act),
+                                  dtype_code(dt), _stream()), "pcs_moe_rows_up")
+    _check(load().pcs_moe_rows_down(a_buf.data_ptr(), w_down.data_ptr(), idx.data_ptr(), y.data_ptr(), P, E, ff, W, dtype_code(dt), _stream()),
            "pcs_moe_rows_down")
     return y, None
 
@@ -568,3 +644,154 @@ def silu_mul(gu: torch.Tensor, ff: int) -> torch.Tensor:
     out = torch.empty(gu.shape[0], ff, dtype=gu.dtype, device=gu.device)
     _check(load().pcs_silu_mul(gu.data_ptr(), gu.stride(0), out.data_ptr(), gu.shape[0], ff, dtype_code(gu.dtype), _stream()), "pcs_silu_mul")
     return out
+
+
+def glu_mul(gu: torch.Tensor, ff: int, act=None) -> torch.Tensor:
+    """act(gu[:, :ff], gu[:, ff:2 ff]) with `act` None (silu(g) * u) or (kind, alpha, limit)."""
+    _cuda(gu)
+    _rows2d(gu, gu.dtype, "glu_mul: gu")
+    out = torch.empty(gu.shape[0], ff, dtype=gu.dtype, device=gu.device)
+    _check(load().pcs_glu_mul(gu.data_ptr(), gu.stride(0), out.data_ptr(), gu.shape[0], ff, _glu(act), dtype_code(gu.dtype), _stream()), "pcs_glu_mul")
+    return out
+
+
+def depth_mix(xs: torch.Tensor, n_terms: int, coef: torch.Tensor, eps: float, x_out: Optional[torch.Tensor] = None, next_w: Optional[torch.Tensor] = None,
+              h_out: Optional[torch.Tensor] = None, w_offset: float = 0.0, rows: Optional[torch.Tensor] = None) -> None:
+    """out = sum_{j < n_terms} coef[j] * xs[j] over float32 xs [terms, T, width] (at the rows `rows` when given); x_out gets the sum,
+    h_out = rms_norm(out) * (w_offset + next_w)."""
+    _cuda(xs, coef, x_out, next_w, h_out, rows)
+    if xs.dtype != torch.float32 or xs.dim() != 3 or not xs.is_contiguous() or not 0 < n_terms <= xs.shape[0]:
+        raise NativeError("depth_mix: xs must be contiguous float32 [terms, T, width]")
+    if coef.dtype != torch.float32 or not coef.is_contiguous() or coef.numel() < n_terms:
+        raise NativeError("depth_mix: coef must be float32 [n_terms]")
+    R = rows.numel() if rows is not None else xs.shape[1]
+    if rows is not None and (rows.dtype != torch.int32 or not rows.is_contiguous()):
+        raise NativeError("depth_mix: rows must be contiguous int32")
+    if x_out is not None and (x_out.dtype != torch.float32 or not x_out.is_contiguous() or tuple(x_out.shape) != (R, xs.shape[2])):
+        raise NativeError("depth_mix: x_out must be contiguous float32 [rows, width]")
+    if next_w is not None and (h_out is None or h_out.dtype != next_w.dtype or not h_out.is_contiguous() or tuple(h_out.shape) != (R, xs.shape[2])
+                               or not next_w.is_contiguous() or next_w.numel() != xs.shape[2]):
+        raise NativeError("depth_mix: h_out must be contiguous [rows, width] in next_w's type")
+    p = pcs_depthmix_params()
+    p.xs, p.term_stride, p.n_terms, p.coef, p.rows = xs.data_ptr(), xs.stride(0), int(n_terms), coef.data_ptr(), _ptr(rows)
+    p.x_out, p.next_w, p.h_out, p.w_offset, p.eps = _ptr(x_out), _ptr(next_w), _ptr(h_out), float(w_offset), float(eps)
+    p.n_rows, p.width, p.dtype = R, xs.shape[2], dtype_code(next_w.dtype if next_w is not None else torch.float32)
+    _check(load().pcs_depth_mix(C.byref(p), _stream()), "pcs_depth_mix")
+
+
+def latent_prep(proj: torch.Tensor, cq_off: int, ckv_off: int, q_rank: int, kv_rank: int, rot_dim: int, cq_norm_w: Optional[torch.Tensor],
+                ckv_norm_w: torch.Tensor, eps: float, freqs: Optional[torch.Tensor], rot_mult: float, cq_out: Optional[torch.Tensor], pool: torch.Tensor,
+                batch: Batch) -> None:
+    """proj [T, *]: the query latent at cq_off, [key/value latent | rotated key part] at ckv_off; pool [slots, 1, cap, kv_rank + rot_dim]."""
+    _cuda(proj, cq_norm_w, ckv_norm_w, freqs, cq_out, pool)
+    dt = proj.dtype
+    _rows2d(proj, dt, "latent_prep: proj")
+    if pool.dtype != dt or not pool.is_contiguous() or pool.dim() != 4 or pool.shape[1] != 1 or pool.shape[3] != kv_rank + rot_dim:
+        raise NativeError("latent_prep: the pool must be contiguous [slots, 1, cap, kv_rank + rot_dim] in the compute type")
+    if cq_out is not None and (cq_out.dtype != dt or not cq_out.is_contiguous() or tuple(cq_out.shape) != (proj.shape[0], q_rank)):
+        raise NativeError("latent_prep: cq_out must be contiguous [T, q_rank]")
+    if rot_dim and (freqs is None or freqs.dtype != torch.float64 or not freqs.is_contiguous() or freqs.numel() < rot_dim // 2):
+        raise NativeError("latent_prep: freqs must be contiguous float64 [rot_dim / 2]")
+    p = pcs_latent_prep_params()
+    p.proj, p.row_stride, p.cq_off, p.ckv_off = proj.data_ptr(), proj.stride(0), int(cq_off), int(ckv_off)
+    p.q_rank, p.kv_rank, p.rot_dim, p.cq_norm_w, p.ckv_norm_w, p.eps = int(q_rank), int(kv_rank), int(rot_dim), _ptr(cq_norm_w), ckv_norm_w.data_ptr(), float(eps)
+    p.freqs, p.rot_mult, p.cq_out, p.pool, p.cap = _ptr(freqs), float(rot_mult), _ptr(cq_out), pool.data_ptr(), pool.shape[2]
+    p.tok_seq, p.tok_pos, p.seq_slot = batch.tok_seq.data_ptr(), batch.tok_pos.data_ptr(), batch.seq_slot.data_ptr()
+    p.n_tokens, p.dtype = batch.n_tokens, dtype_code(dt)
+    _check(load().pcs_latent_prep(C.byref(p), _stream()), "pcs_latent_prep")
+
+
+def latent_q(q: torch.Tensor, n_heads: int, dim: int, rot_dim: int, freqs: Optional[torch.Tensor], rot_mult: float, batch: Batch,
+             q_lat: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """q [T, H * (dim + rot_dim)]: every head's rotated part is turned by the token's position.  Without q_lat in place (q is
+    returned); with q_lat [T, H, kv_rank] (any strides, contiguous last dimension) a new [T, H * (kv_rank + rot_dim)] matrix of
+    [q_lat | rotated part] per head is returned."""
+    _cuda(q, freqs, q_lat)
+    dt = q.dtype
+    if not q.is_contiguous() or q.dim() != 2 or q.shape[1] != n_heads * (dim + rot_dim):
+        raise NativeError("latent_q: q must be contiguous [T, H * (dim + rot_dim)]")
+    p = pcs_latent_q_params()
+    out = q
+    if q_lat is not None:
+        if q_lat.dtype != dt or q_lat.dim() != 3 or q_lat.stride(2) != 1 or q_lat.shape[0] != q.shape[0] or q_lat.shape[1] != n_heads:
+            raise NativeError("latent_q: q_lat must be [T, H, kv_rank] with a contiguous last dimension")
+        out = torch.empty(q.shape[0], n_heads * (q_lat.shape[2] + rot_dim), dtype=dt, device=q.device)
+        p.q_lat, p.lat_tok_stride, p.lat_head_stride, p.kv_rank = q_lat.data_ptr(), q_lat.stride(0), q_lat.stride(1), q_lat.shape[2]
+    p.q, p.q_out, p.n_heads, p.dim, p.rot_dim = q.data_ptr(), out.data_ptr(), int(n_heads), int(dim), int(rot_dim)
+    p.freqs, p.rot_mult, p.tok_pos, p.n_tokens, p.dtype = _ptr(freqs), float(rot_mult), batch.tok_pos.data_ptr(), q.shape[0], dtype_code(dt)
+    _check(load().pcs_latent_q(C.byref(p), _stream()), "pcs_latent_q")
+    return out
+
+
+def latent_gather(pool: torch.Tensor, width: int, ctx: Batch) -> torch.Tensor:
+    """The first `width` numbers of the pool rows of every context token of `ctx` (a Batch whose entries start at position 0)."""
+    _cuda(pool)
+    out = torch.empty(ctx.n_tokens, width, dtype=pool.dtype, device=pool.device)
+    _check(load().pcs_latent_gather(pool.data_ptr(), pool.shape[2], pool.shape[3], int(width), out.data_ptr(), ctx.tok_seq.data_ptr(), ctx.tok_pos.data_ptr(),
+                                    ctx.seq_slot.data_ptr(), ctx.n_tokens, dtype_code(pool.dtype), _stream()), "pcs_latent_gather")
+    return out
+
+
+def latent_expand(kv: torch.Tensor, pool: torch.Tensor, kv_rank: int, rot_dim: int, n_heads: int, dim: int, vdim: int, k_dense: torch.Tensor,
+                  v_dense: torch.Tensor, ctx: Batch) -> None:
+    """kv [N, H * (dim + vdim)] (plain key parts of all heads, then values) of the context tokens -> k_dense [B, H, cap', dim + rot_dim],
+    v_dense [B, H, cap', vdim], indexed by the batch entry."""
+    _cuda(kv, pool, k_dense, v_dense)
+    dt = kv.dtype
+    _rows2d(kv, dt, "latent_expand: kv")
+    if not (k_dense.is_contiguous() and v_dense.is_contiguous()) or k_dense.dtype != dt or v_dense.dtype != dt or pool.dtype != dt \
+            or tuple(k_dense.shape[1:]) != (n_heads, k_dense.shape[2], dim + rot_dim) or tuple(v_dense.shape[1:]) != (n_heads, k_dense.shape[2], vdim):
+        raise NativeError("latent_expand: dense pools must be contiguous [B, H, cap, dim + rot_dim | vdim] in the compute type")
+    p = pcs_latent_expand_params()
+    p.kv, p.kv_stride, p.pool, p.cap, p.kv_rank, p.rot_dim = kv.data_ptr(), kv.stride(0), pool.data_ptr(), pool.shape[2], int(kv_rank), int(rot_dim)
+    p.n_heads, p.dim, p.vdim, p.k_dense, p.v_dense, p.cap_dense = int(n_heads), int(dim), int(vdim), k_dense.data_ptr(), v_dense.data_ptr(), k_dense.shape[2]
+    p.ctx_seq, p.ctx_pos, p.seq_slot, p.n_ctx, p.dtype = ctx.tok_seq.data_ptr(), ctx.tok_pos.data_ptr(), ctx.seq_slot.data_ptr(), ctx.n_tokens, dtype_code(dt)
+    _check(load().pcs_latent_expand(C.byref(p), _stream()), "pcs_latent_expand")
+
+
+def head_gate(o: torch.Tensor, g: torch.Tensor, out: torch.Tensor) -> None:
+    """out[t, h * vdim + c] = o[t, h, c] * sigmoid(g[t, h]); o [T, H, vdim] with any token / head strides."""
+    _cuda(o, g, out)
+    dt = out.dtype
+    if o.dim() != 3 or o.stride(2) != 1 or o.dtype != dt or g.dtype != dt or g.dim() != 2 or g.stride(1) != 1 or not out.is_contiguous():
+        raise NativeError("head_gate: o [T, H, vdim] and g [T, H] with contiguous last dimensions, out contiguous, one type")
+    T, H, V = o.shape
+    _check(load().pcs_head_gate(o.data_ptr(), o.stride(0), o.stride(1), g.data_ptr(), g.stride(0), out.data_ptr(), T, H, V, dtype_code(dt), _stream()),
+           "pcs_head_gate")
+
+
+def gla_decay(a: torch.Tensor, a2: torch.Tensor, a2_b: Optional[torch.Tensor], tau: float) -> torch.Tensor:
+    """float32 [T, channels]: logsigmoid(a2 a + a2_b) / tau; a [T, rank] (row stride free), a2 [channels, rank]."""
+    _cuda(a, a2, a2_b)
+    _rows2d(a, a2.dtype, "gla_decay: a")
+    if not a2.is_contiguous() or a2.shape[1] != a.shape[1] or (a2_b is not None and (a2_b.dtype != torch.float32 or a2_b.numel() != a2.shape[0])):
+        raise NativeError("gla_decay: a2 contiguous [channels, rank], the bias float32 [channels]")
+    ld = torch.empty(a.shape[0], a2.shape[0], dtype=torch.float32, device=a.device)
+    _check(load().pcs_gla_decay(a.data_ptr(), a.stride(0), a2.data_ptr(), _ptr(a2_b), ld.data_ptr(), a.shape[0], a2.shape[0], a2.shape[1], float(tau),
+                                dtype_code(a2.dtype), _stream()), "pcs_gla_decay")
+    return ld
+
+
+def gla_scan(proj: torch.Tensor, offs, ld: torch.Tensor, norm_w: torch.Tensor, out: torch.Tensor, s_pool: torch.Tensor, eps: float, batch: Batch,
+             impl: int = 0) -> None:
+    """proj [T, *] with q / k / v / gate columns at `offs`; ld float32 [T, H * dim] log decays; state pool float32 [slots, H, dim, vdim];
+    out [T, H * vdim]."""
+    _cuda(proj, ld, norm_w, out, s_pool)
+    dt = proj.dtype
+    _rows2d(proj, dt, "gla_scan: proj")
+    if s_pool.dtype != torch.float32 or not s_pool.is_contiguous() or s_pool.dim() != 4 or not out.is_contiguous() or out.dtype != dt:
+        raise NativeError("gla_scan: the state pool must be contiguous float32 [slots, H, dim, vdim], out contiguous in the compute type")
+    H, D, V = s_pool.shape[1:]
+    if ld.dtype != torch.float32 or not ld.is_contiguous() or tuple(ld.shape) != (proj.shape[0], H * D) or norm_w.dtype != dt or norm_w.numel() != V:
+        raise NativeError("gla_scan: ld float32 [T, H * dim], norm_w [vdim] in the compute type")
+    p = pcs_gla_params()
+    p.proj, p.row_stride = proj.data_ptr(), proj.stride(0)
+    p.q_off, p.k_off, p.v_off, p.g_off = offs
+    p.ld, p.norm_w, p.out, p.s_pool = ld.data_ptr(), norm_w.data_ptr(), out.data_ptr(), s_pool.data_ptr()
+    p.heads, p.dim, p.vdim, p.q_scale, p.eps = H, D, V, float(D) ** -0.5, float(eps)
+    p.seq_slot, p.seq_pos0, p.seq_len, p.seq_off = (batch.seq_slot.data_ptr(), batch.seq_pos0.data_ptr(), batch.seq_len.data_ptr(),
+                                                    batch.seq_off.data_ptr())
+    p.n_seqs, p.n_tokens, p.dtype, p.max_len, p.impl = batch.n_seqs, batch.n_tokens, dtype_code(dt), batch.max_len, int(impl)
+    o_raw = torch.empty(batch.n_tokens, H * V, dtype=torch.float32, device=proj.device)
+    p.o_raw = o_raw.data_ptr()
+    _check(load().pcs_gla_scan(C.byref(p), _stream()), "pcs_gla_scan")

@@ -195,12 +195,13 @@ __global__ void __launch_bounds__(kAttnThreads) attn_plain_kernel(const pcs_attn
   float* qs = sm;
   float* ws = sm + p.dim;
   const int t = blockIdx.x, h = blockIdx.y, tid = threadIdx.x;
-  const int b = p.tok_seq[t], pos = p.tok_pos[t], slot = p.seq_slot[b];
+  const int b = p.tok_seq[t], pos = p.tok_pos[t], slot = p.pool_slot ? p.pool_slot[b] : p.seq_slot[b];
   const int g = h / (p.n_heads / p.n_kv_heads);
   const int D = p.dim, V = p.vdim;
+  const long long VS = p.v_row_stride > 0 ? p.v_row_stride : V;   // elements from one key's value row to the next
   const T* q = static_cast<const T*>(p.q) + (static_cast<long long>(t) * p.n_heads + h) * D;
   const T* K = static_cast<const T*>(p.k_pool) + (static_cast<long long>(slot) * p.n_kv_heads + g) * p.cap * D;
-  const T* Vp = static_cast<const T*>(p.v_pool) + (static_cast<long long>(slot) * p.n_kv_heads + g) * p.cap * V;
+  const T* Vp = static_cast<const T*>(p.v_pool) + (static_cast<long long>(slot) * p.n_kv_heads + g) * p.cap * VS;
   for (int i = tid; i < D; i += kAttnThreads) qs[i] = ldf(q + i);
   const float r1 = p.bias_r1 ? p.bias_r1[h] : 0.f, r2 = p.bias_r1 ? p.bias_r2[h] : 0.f;
   // keys are cut into gridDim.z splits of whole tiles; the sink belongs to split 0
@@ -209,7 +210,7 @@ __global__ void __launch_bounds__(kAttnThreads) attn_plain_kernel(const pcs_attn
   const int chunk = ((n_keys + S - 1) / S + kAttnThreads - 1) / kAttnThreads * kAttnThreads;
   const int k_begin = sp * chunk, k_end = min(n_keys, k_begin + chunk);
   const bool sink_here = p.sink && sp == 0;
-  float m = sink_here ? 0.f : -INFINITY, l = sink_here ? 1.f : 0.f;
+  float m = sink_here ? (p.sink_logit ? p.sink_logit[h] : 0.f) : -INFINITY, l = sink_here ? 1.f : 0.f;
   float acc[kAttnMaxVPT] = {0.f, 0.f, 0.f, 0.f};
   const bool vec = (D % Vec<T>::n) == 0;
   __syncthreads();
@@ -247,7 +248,7 @@ __global__ void __launch_bounds__(kAttnThreads) attn_plain_kernel(const pcs_attn
       const int c = tid + u * kAttnThreads;
       if (c < V) {
         float a = acc[u] * f;
-        for (int jj = 0; jj < nt; ++jj) a = fmaf(ws[jj], ldf(Vp + static_cast<long long>(vis.key(j0 + jj)) * V + c), a);
+        for (int jj = 0; jj < nt; ++jj) a = fmaf(ws[jj], ldf(Vp + static_cast<long long>(vis.key(j0 + jj)) * VS + c), a);
         acc[u] = a;
       }
     }
@@ -288,12 +289,13 @@ __global__ void __launch_bounds__(kAttnThreads) attn_decode_kernel(const pcs_att
   float* ws = sm + p.dim;
   float* part_s = ws + kAttnThreads;
   const int t = blockIdx.x, h = blockIdx.y, tid = threadIdx.x;
-  const int b = p.tok_seq[t], pos = p.tok_pos[t], slot = p.seq_slot[b];
+  const int b = p.tok_seq[t], pos = p.tok_pos[t], slot = p.pool_slot ? p.pool_slot[b] : p.seq_slot[b];
   const int g = h / (p.n_heads / p.n_kv_heads);
   const int D = p.dim, V = p.vdim;
+  const long long VS = p.v_row_stride > 0 ? p.v_row_stride : V;   // elements from one key's value row to the next
   const T* q = static_cast<const T*>(p.q) + (static_cast<long long>(t) * p.n_heads + h) * D;
   const T* K = static_cast<const T*>(p.k_pool) + (static_cast<long long>(slot) * p.n_kv_heads + g) * p.cap * D;
-  const T* Vp = static_cast<const T*>(p.v_pool) + (static_cast<long long>(slot) * p.n_kv_heads + g) * p.cap * V;
+  const T* Vp = static_cast<const T*>(p.v_pool) + (static_cast<long long>(slot) * p.n_kv_heads + g) * p.cap * VS;
   for (int i = tid; i < D; i += kAttnThreads) qs[i] = ldf(q + i);
   const float r1 = p.bias_r1 ? p.bias_r1[h] : 0.f, r2 = p.bias_r1 ? p.bias_r2[h] : 0.f;
   const VisibleKeys vis(pos, p.window, p.keep_first);
@@ -304,7 +306,7 @@ __global__ void __launch_bounds__(kAttnThreads) attn_decode_kernel(const pcs_att
   const int CH = V / N, R = kAttnThreads / CH;  // pieces per value row, keys handled side by side
   const int c = tid % CH, r = tid / CH;
   const bool active = r < R;
-  float m = sink_here ? 0.f : -INFINITY;
+  float m = sink_here ? (p.sink_logit ? p.sink_logit[h] : 0.f) : -INFINITY;
   float lsum = (sink_here && tid == 0) ? 1.f : 0.f;
   float acc[N];
 #pragma unroll
@@ -361,10 +363,10 @@ __global__ void __launch_bounds__(kAttnThreads) attn_decode_kernel(const pcs_att
       int jj = r;
       for (; jj + 3 * R < nt; jj += 4 * R) {
         float v0[N], v1[N], v2[N], v3[N];
-        ld16(vr + static_cast<long long>(vis.key(j0 + jj)) * V, v0);
-        ld16(vr + static_cast<long long>(vis.key(j0 + jj + R)) * V, v1);
-        ld16(vr + static_cast<long long>(vis.key(j0 + jj + 2 * R)) * V, v2);
-        ld16(vr + static_cast<long long>(vis.key(j0 + jj + 3 * R)) * V, v3);
+        ld16(vr + static_cast<long long>(vis.key(j0 + jj)) * VS, v0);
+        ld16(vr + static_cast<long long>(vis.key(j0 + jj + R)) * VS, v1);
+        ld16(vr + static_cast<long long>(vis.key(j0 + jj + 2 * R)) * VS, v2);
+        ld16(vr + static_cast<long long>(vis.key(j0 + jj + 3 * R)) * VS, v3);
         const float w0 = ws[jj], w1 = ws[jj + R], w2 = ws[jj + 2 * R], w3 = ws[jj + 3 * R];
 #pragma unroll
         for (int e = 0; e < N; ++e) acc[e] = fmaf(w3, v3[e], fmaf(w2, v2[e], fmaf(w1, v1[e], fmaf(w0, v0[e], acc[e]))));
@@ -372,7 +374,7 @@ __global__ void __launch_bounds__(kAttnThreads) attn_decode_kernel(const pcs_att
       }
       for (; jj < nt; jj += R) {
         float v0[N];
-        ld16(vr + static_cast<long long>(vis.key(j0 + jj)) * V, v0);
+        ld16(vr + static_cast<long long>(vis.key(j0 + jj)) * VS, v0);
         const float w0 = ws[jj];
 #pragma unroll
         for (int e = 0; e < N; ++e) acc[e] = fmaf(w0, v0[e], acc[e]);
@@ -468,6 +470,7 @@ PCS_API int pcs_attn(const pcs_attn_params* p, void* stream) {
               pcs::kAttnThreads * pcs::kAttnMaxVPT);
   PCS_REQUIRE(p->n_heads <= 65535, "pcs_attn: too many heads");
   PCS_REQUIRE((p->bias_r1 == nullptr) == (p->bias_r2 == nullptr), "pcs_attn: the distance bias needs both r1 and r2");
+  PCS_REQUIRE(p->v_row_stride == 0 || p->v_row_stride >= p->vdim, "pcs_attn: the value row stride %d is below vdim %d", p->v_row_stride, p->vdim);
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   if (p->impl == 0) {
     bool handled = false;
@@ -479,7 +482,7 @@ PCS_API int pcs_attn(const pcs_attn_params* p, void* stream) {
   // few tokens over many keys (decoding): the keys are split so that the launch fills the GPU; each split has >= 128 keys
   const int piece = p->dtype == PCS_BF16 ? 8 : 4;
   const bool decode = p->impl == 0 && p->workspace != nullptr && p->dim % piece == 0 && p->vdim % piece == 0 &&
-                      p->vdim / piece <= pcs::kAttnThreads;
+                      p->vdim / piece <= pcs::kAttnThreads && p->v_row_stride % piece == 0;
   int splits = 1;
   if (p->workspace != nullptr && p->max_keys > 512) {
     const long long blocks = static_cast<long long>(p->n_tokens) * p->n_heads;

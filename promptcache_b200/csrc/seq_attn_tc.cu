@@ -69,7 +69,7 @@ __global__ void __launch_bounds__(TC_THREADS, (DP <= 128 && VP <= 128) ? 3 : 1) 
   const int b = rem / p.n_heads, h = rem - b * p.n_heads, q0 = (n_qtiles - 1 - qt) * BM;
   const int len = p.seq_len[b];
   if (q0 >= len) return;
-  const int pos0 = p.seq_pos0[b], off = p.seq_off[b], slot = p.seq_slot[b];
+  const int pos0 = p.seq_pos0[b], off = p.seq_off[b], slot = p.pool_slot ? p.pool_slot[b] : p.seq_slot[b];
   const int g = h / (p.n_heads / p.n_kv_heads), D = p.dim, V = p.vdim;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, grp = lane >> 2, qd = lane & 3;
   const __nv_bfloat16* Kg = static_cast<const __nv_bfloat16*>(p.k_pool) + (static_cast<long long>(slot) * p.n_kv_heads + g) * p.cap * D;
@@ -90,7 +90,7 @@ __global__ void __launch_bounds__(TC_THREADS, (DP <= 128 && VP <= 128) ? 3 : 1) 
   float* T1 = T0 + 144;  // 16 banks away from T0: the odd and the even rows of a warp read different banks
   const float* tp_a = (row_a & 1) ? T0 + (63 - row_a + qd * 2) : T1 + (62 - row_a + qd * 2);
   const float scale2 = p.scale * 1.4426950408889634f;
-  float m_a = p.sink ? 0.f : -INFINITY, m_b = m_a;
+  float m_a = p.sink ? (p.sink_logit ? p.sink_logit[h] * 1.4426950408889634f : 0.f) : -INFINITY, m_b = m_a;  // base-2 domain
   float l_a = (p.sink && qd == 0) ? 1.f : 0.f, l_b = l_a;  // per-thread share of the row sums; the sink's 1 sits in one lane
   float o[VP / 8][4];
 #pragma unroll
@@ -292,7 +292,7 @@ int launch_v(const pcs_attn_params& p, cudaStream_t st) {
 
 int launch_attn_tc(const pcs_attn_params& p, cudaStream_t st, bool* handled) {
   *handled = false;
-  if (p.dtype != PCS_BF16 || p.max_len < 16 || p.dim % 8 != 0 || p.vdim % 8 != 0 || p.dim > 256 || p.vdim > 256) return PCS_OK;
+  if (p.dtype != PCS_BF16 || p.max_len < 16 || (p.v_row_stride != 0 && p.v_row_stride != p.vdim) || p.dim % 8 != 0 || p.vdim % 8 != 0 || p.dim > 256 || p.vdim > 256) return PCS_OK;
   if (!p.seq_pos0 || !p.seq_len || !p.seq_off) return PCS_OK;
   if (static_cast<long long>((p.max_len + BM - 1) / BM) * p.n_seqs * p.n_heads > 0x7fffffffLL) return PCS_OK;
   *handled = true;

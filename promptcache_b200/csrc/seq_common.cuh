@@ -123,5 +123,30 @@ __device__ __forceinline__ float block_max(float v, float* red) {
 
 __device__ __forceinline__ float sigmoidf_(float z) { return 1.f / (1.f + expf(-z)); }
 __device__ __forceinline__ float softplusf_(float z) { return z > 20.f ? z : log1pf(expf(z)); }
+__device__ __forceinline__ float logsigmoidf_(float z) { return fminf(z, 0.f) - log1pf(expf(-fabsf(z))); }
+
+// sine and cosine of pos * f: the angle is formed and reduced modulo 2 pi in 64-bit, then evaluated in 32-bit on [-pi, pi]
+__device__ __forceinline__ void angle_sincos(int pos, double f, float* s, float* c) {
+  const double a = static_cast<double>(pos) * f;
+  const double r = a - 6.283185307179586476925 * rint(a * 0.15915494309189533577);
+  sincosf(static_cast<float>(r), s, c);
+}
+
+// The gated activation of a feed-forward, by value (a kernel argument): PCS_GLU_SILU: silu(g) * u;
+// PCS_GLU_CLAMPED_SWISH: g' = min(g, limit), u' = clamp(u, -limit, limit), g' * sigmoid(alpha * g') * (u' + 1).
+struct GluAct {
+  int kind;
+  float alpha, limit;
+  __host__ GluAct() : kind(PCS_GLU_SILU), alpha(1.f), limit(0.f) {}
+  __host__ explicit GluAct(const pcs_glu_act* a) : kind(a ? a->kind : PCS_GLU_SILU), alpha(a ? a->alpha : 1.f), limit(a ? a->limit : 0.f) {}
+  __device__ __forceinline__ float operator()(float g, float u) const {
+    if (kind == PCS_GLU_CLAMPED_SWISH) {
+      g = fminf(g, limit);
+      u = fminf(fmaxf(u, -limit), limit);
+      return g * sigmoidf_(alpha * g) * (u + 1.f);
+    }
+    return g * sigmoidf_(g) * u;
+  }
+};
 
 }  // namespace pcs

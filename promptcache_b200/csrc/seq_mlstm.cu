@@ -17,8 +17,6 @@
 
 namespace pcs {
 
-__device__ __forceinline__ float logsigmoidf_(float z) { return fminf(z, 0.f) - log1pf(expf(-fabsf(z))); }
-
 template <typename T>
 __global__ void __launch_bounds__(256) mlstm_gates_kernel(const T* __restrict__ h, long long h_stride, const T* __restrict__ w_i,
                                                           const T* __restrict__ w_f, const float* __restrict__ b_i,

@@ -74,6 +74,9 @@ __host__ __device__ __forceinline__ bool aligned16(const void* q) { return (rein
 __device__ __forceinline__ void route_select(const pcs_route_params& p, int t, int lane, float* z, float* c, float* gs) {
   const int E = p.n_outputs;
   float m = -INFINITY;
+  if (p.bias) {
+    for (int e = lane; e < E; e += 32) z[e] += p.bias[e];
+  }
   for (int e = lane; e < E; e += 32) m = fmaxf(m, z[e]);
   m = warp_max(m);
   float sum = 0.f;
@@ -120,6 +123,13 @@ __device__ __forceinline__ void route_select(const pcs_route_params& p, int t, i
       c[e] = -INFINITY;
     }
     __syncwarp();
+  }
+  if (p.renorm && lane == 0) {  // the softmax over the chosen outputs alone: their scores divided by their sum, in the order of the choices
+    float* w = p.wgt + static_cast<long long>(t) * p.top;
+    float sum_k = 0.f;
+    for (int k = 0; k < p.top; ++k) sum_k += w[k];
+    const float inv_k = 1.f / sum_k;
+    for (int k = 0; k < p.top; ++k) w[k] *= inv_k;
   }
 }
 
@@ -178,7 +188,7 @@ __global__ void __launch_bounds__(256) moe_route_warp_kernel(const pcs_route_par
 template <typename T>
 __global__ void __launch_bounds__(128) moe_rows_up_kernel(const T* __restrict__ h, long long h_stride, const T* __restrict__ w_gu,
                                                           const int32_t* __restrict__ idx, T* __restrict__ act, int top, int n_experts,
-                                                          int ff, int K, bool vec) {
+                                                          int ff, int K, bool vec, const GluAct glu) {
   const int pr = blockIdx.x, e = idx[pr];
   if (e >= n_experts || e < 0) return;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -191,7 +201,7 @@ __global__ void __launch_bounds__(128) moe_rows_up_kernel(const T* __restrict__ 
     if (n >= ff) return;
     const float g = warp_dot(x, wg + static_cast<long long>(n) * K, K, lane, vec);
     const float v = warp_dot(x, wu + static_cast<long long>(n) * K, K, lane, vec);
-    if (lane == 0) stf(act + static_cast<long long>(pr) * ff + n, g * sigmoidf_(g) * v);
+    if (lane == 0) stf(act + static_cast<long long>(pr) * ff + n, glu(g, v));
   }
 }
 
@@ -272,7 +282,7 @@ __global__ void __launch_bounds__(256) moe_combine_kernel(const pcs_combine_para
 }
 
 template <typename T, bool VEC>
-__global__ void __launch_bounds__(256) silu_mul_kernel(const T* __restrict__ gu, long long gu_stride, T* __restrict__ out, int ff) {
+__global__ void __launch_bounds__(256) silu_mul_kernel(const T* __restrict__ gu, long long gu_stride, T* __restrict__ out, int ff, const GluAct glu) {
   constexpr int N = Vec<T>::n;
   const int r = blockIdx.x;
   const T* g = gu + r * gu_stride;
@@ -283,13 +293,13 @@ __global__ void __launch_bounds__(256) silu_mul_kernel(const T* __restrict__ gu,
       ld16(g + i, a);
       ld16(g + ff + i, u);
 #pragma unroll
-      for (int e = 0; e < N; ++e) a[e] = a[e] * sigmoidf_(a[e]) * u[e];
+      for (int e = 0; e < N; ++e) a[e] = glu(a[e], u[e]);
       st16(o + i, a);
     }
   } else {
     for (int i = blockIdx.y * 256 + threadIdx.x; i < ff; i += gridDim.y * 256) {
       const float a = ldf(g + i);
-      stf(o + i, a * sigmoidf_(a) * ldf(g + ff + i));
+      stf(o + i, glu(a, ldf(g + ff + i)));
     }
   }
 }
@@ -317,7 +327,7 @@ PCS_API int pcs_moe_route(const pcs_route_params* p, void* stream) {
 }
 
 PCS_API int pcs_moe_rows_up(const void* h, int64_t h_stride, const void* w_gu, const int32_t* idx, void* act, int n_pairs, int top, int n_experts,
-                            int ff, int width, int dtype, void* stream) {
+                            int ff, int width, const pcs_glu_act* glu, int dtype, void* stream) {
   if (n_pairs == 0 || n_experts == 0) return PCS_OK;
   PCS_REQUIRE(h && w_gu && idx && act && n_pairs > 0 && top > 0 && ff > 0 && width > 0, "pcs_moe_rows_up: bad arguments");
   const long long esz = dtype == PCS_BF16 ? 2 : 4;
@@ -325,7 +335,7 @@ PCS_API int pcs_moe_rows_up(const void* h, int64_t h_stride, const void* w_gu, c
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   dim3 grid(n_pairs, (ff + 7) / 8);
   PCS_DISPATCH(dtype, pcs::moe_rows_up_kernel<T><<<grid, 128, 0, st>>>(static_cast<const T*>(h), h_stride, static_cast<const T*>(w_gu), idx,
-                                                                       static_cast<T*>(act), top, n_experts, ff, width, vec));
+                                                                       static_cast<T*>(act), top, n_experts, ff, width, vec, pcs::GluAct(glu)));
   PCS_CHECK_CUDA(cudaGetLastError());
   pcs::count_launch();
   return PCS_OK;
@@ -365,15 +375,21 @@ PCS_API int pcs_moe_combine(const pcs_combine_params* p, void* stream) {
 }
 
 PCS_API int pcs_silu_mul(const void* gu, int64_t gu_stride, void* out, int n_rows, int ff, int dtype, void* stream) {
+  return pcs_glu_mul(gu, gu_stride, out, n_rows, ff, nullptr, dtype, stream);
+}
+
+PCS_API int pcs_glu_mul(const void* gu, int64_t gu_stride, void* out, int n_rows, int ff, const pcs_glu_act* glu, int dtype, void* stream) {
   if (n_rows == 0 || ff == 0) return PCS_OK;
-  PCS_REQUIRE(gu && out && n_rows > 0 && ff > 0, "pcs_silu_mul: bad arguments");
+  PCS_REQUIRE(gu && out && n_rows > 0 && ff > 0, "pcs_glu_mul: bad arguments");
+  PCS_REQUIRE(glu == nullptr || glu->kind == PCS_GLU_SILU || glu->kind == PCS_GLU_CLAMPED_SWISH, "pcs_glu_mul: unknown activation %d", glu->kind);
+  const pcs::GluAct act(glu);
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   const int piece = dtype == PCS_BF16 ? 8 : 4;
   const long long esz = dtype == PCS_BF16 ? 2 : 4;
   const bool vec = ff % piece == 0 && (gu_stride * esz) % 16 == 0 && pcs::aligned16(gu) && pcs::aligned16(out);
   dim3 grid(n_rows, vec ? (ff / piece + 255) / 256 : (ff + 1023) / 1024);
-  if (vec) PCS_DISPATCH(dtype, (pcs::silu_mul_kernel<T, true><<<grid, 256, 0, st>>>(static_cast<const T*>(gu), gu_stride, static_cast<T*>(out), ff)));
-  else PCS_DISPATCH(dtype, (pcs::silu_mul_kernel<T, false><<<grid, 256, 0, st>>>(static_cast<const T*>(gu), gu_stride, static_cast<T*>(out), ff)));
+  if (vec) PCS_DISPATCH(dtype, (pcs::silu_mul_kernel<T, true><<<grid, 256, 0, st>>>(static_cast<const T*>(gu), gu_stride, static_cast<T*>(out), ff, act)));
+  else PCS_DISPATCH(dtype, (pcs::silu_mul_kernel<T, false><<<grid, 256, 0, st>>>(static_cast<const T*>(gu), gu_stride, static_cast<T*>(out), ff, act)));
   PCS_CHECK_CUDA(cudaGetLastError());
   pcs::count_launch();
   return PCS_OK;

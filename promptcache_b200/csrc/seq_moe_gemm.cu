@@ -89,7 +89,7 @@ __global__ void __launch_bounds__(128) moe_gather_kernel(const uint4* __restrict
 template <int STAGE>
 __global__ void __launch_bounds__(G_THREADS, 2) moe_gemm_kernel(const __nv_bfloat16* __restrict__ a, long long a_stride, const __nv_bfloat16* __restrict__ w,
                                                                 const int32_t* __restrict__ plan, void* __restrict__ out, int n_pairs, int top, int E,
-                                                                int ff, int W) {
+                                                                int ff, int W, const GluAct glu) {
   constexpr int LD = GK + GPAD;                         // row length in shared memory
   constexpr int TILE = GM * LD;                         // elements of one A (or B) tile
   extern __shared__ __align__(16) unsigned char smem_raw[];
@@ -201,7 +201,7 @@ __global__ void __launch_bounds__(G_THREADS, 2) moe_gemm_kernel(const __nv_bfloa
           const float g0 = acc[i][j][half * 2], g1 = acc[i][j][half * 2 + 1];
           const float u0 = acc[i][4 + j][half * 2], u1 = acc[i][4 + j][half * 2 + 1];
           __nv_bfloat16* o = static_cast<__nv_bfloat16*>(out) + static_cast<long long>(row0 + r) * ff + n;
-          *reinterpret_cast<uint32_t*>(o) = pack_bf16(g0 * sigmoidf_(g0) * u0, g1 * sigmoidf_(g1) * u1);
+          *reinterpret_cast<uint32_t*>(o) = pack_bf16(glu(g0, u0), glu(g1, u1));
         }
       } else {
 #pragma unroll
@@ -257,7 +257,7 @@ PCS_API int pcs_moe_gather(const void* h, int64_t h_stride, const int32_t* plan,
 }
 
 PCS_API int pcs_moe_gemm(int stage, const void* a, int64_t a_stride, const void* w, const int32_t* plan, void* out, int n_pairs, int top,
-                         int n_experts, int ff, int width, void* stream) {
+                         int n_experts, int ff, int width, const pcs_glu_act* glu, void* stream) {
   if (n_pairs == 0 || n_experts == 0) return PCS_OK;
   PCS_REQUIRE(a && w && plan && out && n_pairs > 0 && top > 0 && ff > 0 && width > 0 && (stage == 0 || stage == 1), "pcs_moe_gemm: bad arguments");
   PCS_REQUIRE(ff % 8 == 0 && width % 8 == 0 && a_stride % 8 == 0 && (reinterpret_cast<uintptr_t>(a) & 15) == 0 && (reinterpret_cast<uintptr_t>(w) & 15) == 0,
@@ -272,10 +272,11 @@ PCS_API int pcs_moe_gemm(int stage, const void* a, int64_t a_stride, const void*
     configured = true;
   }
   PCS_REQUIRE(grid.y <= 65535, "pcs_moe_gemm: too many output features");
+  const pcs::GluAct act(glu);
   const __nv_bfloat16* ap = static_cast<const __nv_bfloat16*>(a);
   const __nv_bfloat16* wp = static_cast<const __nv_bfloat16*>(w);
-  if (stage == 0) pcs::moe_gemm_kernel<0><<<grid, pcs::G_THREADS, pcs::G_SMEM, st>>>(ap, a_stride, wp, plan, out, n_pairs, top, n_experts, ff, width);
-  else pcs::moe_gemm_kernel<1><<<grid, pcs::G_THREADS, pcs::G_SMEM, st>>>(ap, a_stride, wp, plan, out, n_pairs, top, n_experts, ff, width);
+  if (stage == 0) pcs::moe_gemm_kernel<0><<<grid, pcs::G_THREADS, pcs::G_SMEM, st>>>(ap, a_stride, wp, plan, out, n_pairs, top, n_experts, ff, width, act);
+  else pcs::moe_gemm_kernel<1><<<grid, pcs::G_THREADS, pcs::G_SMEM, st>>>(ap, a_stride, wp, plan, out, n_pairs, top, n_experts, ff, width, act);
   PCS_CHECK_CUDA(cudaGetLastError());
   pcs::count_launch();
   return PCS_OK;

@@ -53,13 +53,14 @@ __global__ void __launch_bounds__(256) gate_norm_add_kernel(const pcs_gna_params
   __shared__ float red[33];
   const int r = blockIdx.x, W = p.width;
   const T* y = static_cast<const T*>(p.y) + static_cast<long long>(r) * p.y_stride;
+  const float* y32 = p.y_f32 ? static_cast<const float*>(p.y) + static_cast<long long>(r) * p.y_stride : nullptr;
   const T* g = p.g ? static_cast<const T*>(p.g) + static_cast<long long>(r) * p.g_stride : nullptr;
   const T* w = static_cast<const T*>(p.w);
   const T* ls = static_cast<const T*>(p.ls);
   float* x = p.x + static_cast<long long>(r) * W;
   float ss = 0.f;
   for (int i = threadIdx.x; i < W; i += blockDim.x) {
-    float v = ldf(y + i);
+    float v = y32 ? y32[i] : ldf(y + i);
     if (g) v *= sigmoidf_(ldf(g + i));
     u[i] = v;
     ss = fmaf(v, v, ss);
@@ -68,7 +69,7 @@ __global__ void __launch_bounds__(256) gate_norm_add_kernel(const pcs_gna_params
   const float inv = 1.f / sqrtf(ss / static_cast<float>(W) + p.eps);
   float s2 = 0.f;
   for (int i = threadIdx.x; i < W; i += blockDim.x) {
-    float v = u[i] * inv * ldf(w + i);
+    float v = u[i] * inv * (p.w_offset + ldf(w + i));
     if (ls) v *= ldf(ls + i);
     const float xn = x[i] + v;
     x[i] = xn;
@@ -80,7 +81,7 @@ __global__ void __launch_bounds__(256) gate_norm_add_kernel(const pcs_gna_params
   const float inv2 = 1.f / sqrtf(s2 / static_cast<float>(W) + p.eps);
   const T* nw = static_cast<const T*>(p.next_w);
   T* h = static_cast<T*>(p.h_out) + static_cast<long long>(r) * W;
-  for (int i = threadIdx.x; i < W; i += blockDim.x) stf(h + i, u[i] * inv2 * ldf(nw + i));
+  for (int i = threadIdx.x; i < W; i += blockDim.x) stf(h + i, u[i] * inv2 * (p.w_offset + ldf(nw + i)));
 }
 
 // The same row operation for rows of at most 256 * PPT 16-byte pieces whose pointers and strides are 16-byte aligned: a
@@ -131,7 +132,7 @@ __global__ void __launch_bounds__(256) gate_norm_add_vec_kernel(const pcs_gna_pa
     if (i < W) {
 #pragma unroll
       for (int e = 0; e < N; ++e) {
-        float t = v[u][e] * inv * wv[u][e];
+        float t = v[u][e] * inv * (p.w_offset + wv[u][e]);
         if (ls) t *= lv[u][e];
         xv[u][e] += t;
         s2 = fmaf(xv[u][e], xv[u][e], s2);
@@ -149,7 +150,7 @@ __global__ void __launch_bounds__(256) gate_norm_add_vec_kernel(const pcs_gna_pa
     if (i < W) {
       float o[N];
 #pragma unroll
-      for (int e = 0; e < N; ++e) o[e] = xv[u][e] * inv2 * nv[u][e];
+      for (int e = 0; e < N; ++e) o[e] = xv[u][e] * inv2 * (p.w_offset + nv[u][e]);
       st16(h + i, o);
     }
   }
@@ -187,7 +188,66 @@ __global__ void __launch_bounds__(256) xielu_kernel(const T* __restrict__ z, lon
   }
 }
 
+// One block per row: the weighted sum of the terms' rows in shared memory, then the norm.
+template <typename T>
+__global__ void __launch_bounds__(256) depth_mix_kernel(const pcs_depthmix_params p) {
+  extern __shared__ float u[];  // [width]
+  __shared__ float red[33];
+  const int r = blockIdx.x, W = p.width;
+  const long long row = p.rows ? p.rows[r] : r;
+  const float* src = p.xs + row * W;
+  const bool vec = (W & 3) == 0 && (p.term_stride & 3) == 0 && (reinterpret_cast<uintptr_t>(p.xs) & 15) == 0;
+  float ss = 0.f;
+  if (vec) {
+    for (int i = threadIdx.x * 4; i < W; i += blockDim.x * 4) {
+      float4 a = make_float4(0.f, 0.f, 0.f, 0.f);
+      for (int j = 0; j < p.n_terms; ++j) {
+        const float c = p.coef[j];
+        const float4 v = *reinterpret_cast<const float4*>(src + j * p.term_stride + i);
+        a.x = fmaf(c, v.x, a.x); a.y = fmaf(c, v.y, a.y); a.z = fmaf(c, v.z, a.z); a.w = fmaf(c, v.w, a.w);
+      }
+      u[i] = a.x; u[i + 1] = a.y; u[i + 2] = a.z; u[i + 3] = a.w;
+      ss = fmaf(a.x, a.x, fmaf(a.y, a.y, fmaf(a.z, a.z, fmaf(a.w, a.w, ss))));
+    }
+  } else {
+    for (int i = threadIdx.x; i < W; i += blockDim.x) {
+      float a = 0.f;
+      for (int j = 0; j < p.n_terms; ++j) a = fmaf(p.coef[j], src[j * p.term_stride + i], a);
+      u[i] = a;
+      ss = fmaf(a, a, ss);
+    }
+  }
+  __syncthreads();
+  if (p.x_out) {
+    float* xo = p.x_out + static_cast<long long>(r) * W;
+    for (int i = threadIdx.x; i < W; i += blockDim.x) xo[i] = u[i];
+  }
+  if (p.next_w == nullptr) return;
+  ss = block_sum(ss, red);
+  const float inv = 1.f / sqrtf(ss / static_cast<float>(W) + p.eps);
+  const T* nw = static_cast<const T*>(p.next_w);
+  T* h = static_cast<T*>(p.h_out) + static_cast<long long>(r) * W;
+  for (int i = threadIdx.x; i < W; i += blockDim.x) stf(h + i, u[i] * inv * (p.w_offset + ldf(nw + i)));
+}
+
 }  // namespace pcs
+
+PCS_API int pcs_depth_mix(const pcs_depthmix_params* p, void* stream) {
+  PCS_REQUIRE(p, "pcs_depth_mix: null params");
+  if (p->n_rows == 0) return PCS_OK;
+  PCS_REQUIRE(p->xs && p->coef && p->n_terms > 0 && p->n_rows > 0 && p->width > 0, "pcs_depth_mix: bad arguments");
+  PCS_REQUIRE(p->x_out || p->next_w, "pcs_depth_mix: nothing to write");
+  PCS_REQUIRE(p->next_w == nullptr || p->h_out != nullptr, "pcs_depth_mix: next_w needs h_out");
+  const size_t smem = static_cast<size_t>(p->width) * sizeof(float);
+  PCS_REQUIRE(smem <= 200 * 1024, "pcs_depth_mix: width %d exceeds the shared-memory row", p->width);
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (smem > 48 * 1024)
+    PCS_DISPATCH(p->dtype, PCS_CHECK_CUDA(cudaFuncSetAttribute(pcs::depth_mix_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024)));
+  PCS_DISPATCH(p->dtype, pcs::depth_mix_kernel<T><<<p->n_rows, 256, smem, st>>>(*p));
+  PCS_CHECK_CUDA(cudaGetLastError());
+  pcs::count_launch();
+  return PCS_OK;
+}
 
 PCS_API int pcs_version(void) { return PCS_ABI_VERSION; }
 PCS_API const char* pcs_last_error(void) { return pcs::g_err; }
@@ -231,7 +291,7 @@ PCS_API int pcs_gate_norm_add(const pcs_gna_params* p, void* stream) {
   const int piece = p->dtype == PCS_BF16 ? 8 : 4;
   const long long esz = p->dtype == PCS_BF16 ? 2 : 4;
   auto al = [](const void* q) { return (reinterpret_cast<uintptr_t>(q) & 15) == 0; };
-  const bool vec = p->width % piece == 0 && p->width <= 512 * piece && (p->y_stride * esz) % 16 == 0 && al(p->x) && al(p->y) && al(p->w) &&
+  const bool vec = !p->y_f32 && p->width % piece == 0 && p->width <= 512 * piece && (p->y_stride * esz) % 16 == 0 && al(p->x) && al(p->y) && al(p->w) &&
                    (p->g == nullptr || (al(p->g) && (p->g_stride * esz) % 16 == 0)) && (p->ls == nullptr || al(p->ls)) &&
                    (p->next_w == nullptr || (al(p->next_w) && al(p->h_out)));
   if (vec) {

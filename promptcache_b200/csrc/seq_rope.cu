@@ -10,12 +10,6 @@
 
 namespace pcs {
 
-__device__ __forceinline__ void angle_sincos(int pos, double f, float* s, float* c) {
-  const double a = static_cast<double>(pos) * f;
-  const double r = a - 6.283185307179586476925 * rint(a * 0.15915494309189533577);
-  sincosf(static_cast<float>(r), s, c);
-}
-
 constexpr int kMaxRotPairs = 256;  // rot_dims <= 512
 
 // src: `heads` heads of `dim` coordinates; dst(head) gives the head's destination; sc: the token's (sin, cos) per pair

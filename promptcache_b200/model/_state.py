@@ -6,6 +6,8 @@ carried from token to token) keeps its sequences in a `SlotPool` instead: every 
 layer has pool tensors whose first dimension is the slot,
 
     attention layer   K [slots, Hkv, cap, dim]   V [slots, Hkv, cap, vdim]        (compute type)
+    low-rank attention  CKV [slots, 1, cap, rank + rot_dim]                        (compute type)
+    decaying matrix   S [slots, H, dim, vdim]                                      (float32)
     matrix memory     S [slots, H, dim, vdim]    n [slots, H, dim]    m [slots, H]  (float32)
     short convolution tail [slots, 2, taps - 1, width]                             (float32, double-buffered)
 
@@ -36,6 +38,21 @@ class KVSpec:
 @dataclass(frozen=True)
 class MatrixMemorySpec:
     """A matrix-memory recurrent layer's state: per head a dim x vdim matrix, a dim vector and a scalar."""
+    heads: int
+    dim: int
+    vdim: int
+
+
+@dataclass(frozen=True)
+class LatentKVSpec:
+    """A low-rank attention layer's rows: per token ONE row [latent (rank) | rotated key part (rot_dim)] for all heads."""
+    rank: int
+    rot_dim: int
+
+
+@dataclass(frozen=True)
+class DecayStateSpec:
+    """A gated linear-attention layer's state: per head a dim x vdim matrix whose rows decay."""
     heads: int
     dim: int
     vdim: int
@@ -79,6 +96,10 @@ class SlotPool:
         if isinstance(spec, KVSpec):
             return {"k": torch.zeros(n_slots, spec.n_kv_heads, cap, spec.dim, dtype=self.dtype, device=self.device),
                     "v": torch.zeros(n_slots, spec.n_kv_heads, cap, spec.vdim, dtype=self.dtype, device=self.device)}
+        if isinstance(spec, LatentKVSpec):
+            return {"ckv": torch.zeros(n_slots, 1, cap, spec.rank + spec.rot_dim, dtype=self.dtype, device=self.device)}
+        if isinstance(spec, DecayStateSpec):
+            return {"s": torch.zeros(n_slots, spec.heads, spec.dim, spec.vdim, dtype=torch.float32, device=self.device)}
         if isinstance(spec, MatrixMemorySpec):
             return {"s": torch.zeros(n_slots, spec.heads, spec.dim, spec.vdim, dtype=torch.float32, device=self.device),
                     "n": torch.zeros(n_slots, spec.heads, spec.dim, dtype=torch.float32, device=self.device),
@@ -91,7 +112,7 @@ class SlotPool:
         for spec, old in zip(self.specs, self.layers):
             new = self._alloc(spec, n_slots, cap)
             for name, t in old.items():  # carry every slot over (released ones hold nothing anybody reads)
-                if name in ("k", "v"):
+                if name in ("k", "v", "ckv"):
                     new[name][:old_slots, :, :old_cap].copy_(t)
                 else:
                     new[name][:old_slots].copy_(t)
