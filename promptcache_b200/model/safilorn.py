@@ -207,7 +207,8 @@ class SafilornForCausalLM(SlotPoolCausalLM):
         nsq.latent_prep(proj, blk["offs"][0], blk["offs"][1], Q, C, R, blk["cq_norm"], blk["ckv_norm"], self.eps, blk["freqs"], blk["rot_mult"], cq,
                         pool["ckv"], batch)
         q = nsq.linear(cq, blk["w_uq"])                      # [T, H * (D + R)], per head [plain | rotated]
-        form = self.latent_form or ("expanded" if batch.max_len >= self.expand_min_len and not torch.cuda.is_current_stream_capturing() else "latent")
+        # a recorded decoding step reads everything that changes from device buffers: only the latent form does
+        form = "latent" if torch.cuda.is_current_stream_capturing() else (self.latent_form or ("expanded" if batch.max_len >= self.expand_min_len else "latent"))
         if form == "expanded":
             ctx, ids = self._context(batch, step)
             c_ctx = nsq.latent_gather(pool["ckv"], C, ctx)
