@@ -436,6 +436,47 @@ typedef struct pcs_gla_params {
 } pcs_gla_params;
 int pcs_gla_scan(const pcs_gla_params* p, void* stream);
 
+/* The same recurrence in chunks of `chunk` tokens (prompts).  The step's entries are cut into chunks (an entry's last one may
+ * be short); chunk c holds tokens chunk_first[c] .. chunk_first[c] + chunk_len[c] - 1 of the concatenated matrix.  With B_i the
+ * running sum of the log decays inside a chunk (per key channel) and e its last token:
+ *   pcs_gla_chunk_prep   qd[c, h, i, :] = q_i * q_scale * exp(B_i)        kd[c, h, i, :] = k_i * exp(B_e - B_i)     (fp32 [chunks, H, chunk, dim])
+ *                        g[c, h, :] = exp(B_e)                            vf[c, h, i, :] = v_i                      (fp32; rows past the chunk are zero)
+ *                        a[c, h, i, s] = sum_d q_i[d] k_s[d] exp(B_i[d] - B_s[d]) for s <= i, else 0     (fp32 [chunks, H, chunk, chunk]; every exponent <= 0)
+ *   (the caller forms u[c, h] = kd[c, h]^T vf[c, h], fp32 [chunks, H, dim, vdim], with a matrix product)
+ *   pcs_gla_chunk_scan   per entry, over its chunks in order: u[c] is replaced by the state S the chunk starts from, S <- g[c] * S + u[c];
+ *                        S starts from the pool (zero for an entry whose slot holds no tokens) and returns there
+ *   (the caller forms o[c, h] = qd[c, h] S[c, h] + a[c, h] vf[c, h], fp32 [chunks, H, chunk, vdim])
+ *   pcs_gla_chunk_out    out[t, h, :] = o_t / sqrt(mean(o_t^2) + eps) * norm_w * silu(g[t, h, :]), o_t = o[tok_row[t] / chunk, h, tok_row[t] % chunk, :] */
+typedef struct pcs_gla_chunk_params {
+  const void* proj;
+  int64_t row_stride;
+  int32_t q_off, k_off, v_off, g_off;
+  const float* ld;
+  int32_t heads, dim, vdim, chunk;
+  float q_scale, eps;
+  const int32_t* chunk_first;  /* [n_chunks] */
+  const int32_t* chunk_len;    /* [n_chunks] */
+  int32_t n_chunks, n_tokens, dtype, n_seqs;
+  float* qd;
+  float* kd;
+  float* g;
+  float* vf;
+  float* a;
+  float* u;                    /* [n_chunks, H, dim, vdim]: the chunks' own sums on entry of the scan, their start states after it */
+  float* s_pool;
+  const int32_t* seq_slot;
+  const int32_t* seq_pos0;
+  const int32_t* seq_chunk0;   /* [n_seqs] first chunk of the entry */
+  const int32_t* seq_chunks;   /* [n_seqs] number of its chunks */
+  const float* o;              /* [n_chunks, H, chunk, vdim] */
+  const int32_t* tok_row;      /* [n_tokens]: chunk index * chunk + place in the chunk */
+  const void* norm_w;
+  void* out;
+} pcs_gla_chunk_params;
+int pcs_gla_chunk_prep(const pcs_gla_chunk_params* p, void* stream);
+int pcs_gla_chunk_scan(const pcs_gla_chunk_params* p, void* stream);
+int pcs_gla_chunk_out(const pcs_gla_chunk_params* p, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

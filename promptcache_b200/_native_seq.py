@@ -19,7 +19,7 @@ PCS_BF16, PCS_F32 = 0, 1
 EXPORTS = ("pcs_version", "pcs_last_error", "pcs_launch_count", "pcs_attn_workspace_floats", "pcs_embed", "pcs_rmsnorm", "pcs_gate_norm_add", "pcs_xielu", "pcs_linear_rows",
            "pcs_qk_prep", "pcs_attn", "pcs_mlstm_gates", "pcs_mlstm_scan", "pcs_embed_bigram", "pcs_norm_conv", "pcs_rope_kv_prep", "pcs_moe_route",
            "pcs_moe_rows_up", "pcs_moe_rows_down", "pcs_moe_plan", "pcs_moe_gather", "pcs_moe_gemm", "pcs_moe_combine", "pcs_silu_mul", "pcs_glu_mul",
-           "pcs_depth_mix", "pcs_latent_prep", "pcs_latent_q", "pcs_latent_gather", "pcs_latent_expand", "pcs_head_gate", "pcs_gla_decay", "pcs_gla_scan")
+           "pcs_depth_mix", "pcs_latent_prep", "pcs_latent_q", "pcs_latent_gather", "pcs_latent_expand", "pcs_head_gate", "pcs_gla_decay", "pcs_gla_scan", "pcs_gla_chunk_prep", "pcs_gla_chunk_scan", "pcs_gla_chunk_out")
 GLU_SILU, GLU_CLAMPED_SWISH = 0, 1
 
 
@@ -113,6 +113,15 @@ class pcs_gla_params(C.Structure):
                 ("n_seqs", C.c_int32), ("n_tokens", C.c_int32), ("dtype", C.c_int32), ("max_len", C.c_int32), ("impl", C.c_int32), ("o_raw", C.c_void_p)]
 
 
+class pcs_gla_chunk_params(C.Structure):
+    _fields_ = [("proj", C.c_void_p), ("row_stride", C.c_int64), ("q_off", C.c_int32), ("k_off", C.c_int32), ("v_off", C.c_int32), ("g_off", C.c_int32),
+                ("ld", C.c_void_p), ("heads", C.c_int32), ("dim", C.c_int32), ("vdim", C.c_int32), ("chunk", C.c_int32), ("q_scale", C.c_float), ("eps", C.c_float),
+                ("chunk_first", C.c_void_p), ("chunk_len", C.c_void_p), ("n_chunks", C.c_int32), ("n_tokens", C.c_int32), ("dtype", C.c_int32), ("n_seqs", C.c_int32),
+                ("qd", C.c_void_p), ("kd", C.c_void_p), ("g", C.c_void_p), ("vf", C.c_void_p), ("a", C.c_void_p), ("u", C.c_void_p), ("s_pool", C.c_void_p),
+                ("seq_slot", C.c_void_p), ("seq_pos0", C.c_void_p), ("seq_chunk0", C.c_void_p), ("seq_chunks", C.c_void_p), ("o", C.c_void_p), ("tok_row", C.c_void_p),
+                ("norm_w", C.c_void_p), ("out", C.c_void_p)]
+
+
 class pcs_combine_params(C.Structure):
     _fields_ = [("x", C.c_void_p), ("y", C.c_void_p), ("idx", C.c_void_p), ("wgt", C.c_void_p), ("h", C.c_void_p), ("h_stride", C.c_int64),
                 ("ys", C.c_void_p), ("ys_stride", C.c_int64), ("shared_gate", C.c_void_p), ("mult", C.c_float),
@@ -190,6 +199,8 @@ def load() -> C.CDLL:
     lib.pcs_head_gate.argtypes = [C.c_void_p, C.c_int64, C.c_int64, C.c_void_p, C.c_int64, C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_int, C.c_void_p]
     lib.pcs_gla_decay.argtypes = [C.c_void_p, C.c_int64, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_float, C.c_int, C.c_void_p]
     lib.pcs_gla_scan.argtypes = [C.POINTER(pcs_gla_params), C.c_void_p]
+    for name in ("pcs_gla_chunk_prep", "pcs_gla_chunk_scan", "pcs_gla_chunk_out"):
+        getattr(lib, name).argtypes = [C.POINTER(pcs_gla_chunk_params), C.c_void_p]
     for name in EXPORTS[4:]:
         getattr(lib, name).restype = C.c_int
     _lib = lib
@@ -772,10 +783,66 @@ def gla_decay(a: torch.Tensor, a2: torch.Tensor, a2_b: Optional[torch.Tensor], t
     return ld
 
 
+GLA_CHUNK = 64          # tokens per chunk of the chunkwise form
+GLA_CHUNK_MIN_LEN = 32  # steps whose longest entry brings fewer tokens go token by token (decoding, tails of a prompt)
+
+
+def _gla_chunk_plan(batch: Batch, chunk: int):
+    """The step's entries cut into chunks, as device arrays (made once per step and kept on the batch)."""
+    plan = getattr(batch, "_gla_plan", None)
+    if plan is not None and plan["chunk"] == chunk:
+        return plan
+    first, length, seq0, seqn, tok_row = [], [], [], [], []
+    for off, n in zip(batch.offsets, batch.lens):
+        seq0.append(len(first))
+        seqn.append((n + chunk - 1) // chunk)
+        for c in range(0, n, chunk):
+            tok_row += range(len(first) * chunk, len(first) * chunk + min(chunk, n - c))
+            first.append(off + c)
+            length.append(min(chunk, n - c))
+    nc = len(first)
+    host = torch.tensor(first + length + seq0 + seqn + tok_row, dtype=torch.int32)
+    dev = host.pin_memory().to(batch.meta.device, non_blocking=True)
+    B = batch.n_seqs
+    plan = {"chunk": chunk, "n_chunks": nc, "first": dev[:nc], "len": dev[nc:2 * nc], "seq0": dev[2 * nc:2 * nc + B], "seqn": dev[2 * nc + B:2 * nc + 2 * B],
+            "tok_row": dev[2 * nc + 2 * B:], "all": dev}
+    batch._gla_plan = plan
+    return plan
+
+
+def gla_scan_chunked(proj: torch.Tensor, offs, ld: torch.Tensor, norm_w: torch.Tensor, out: torch.Tensor, s_pool: torch.Tensor, eps: float, batch: Batch,
+                     chunk: int = GLA_CHUNK) -> None:
+    """The recurrence of `gla_scan` in chunks: the factors that carry decays are formed by `pcs_gla_chunk_prep` (32-bit, every
+    exponent <= 0), the sums over tokens and channels are three batched float32 matrix products, the chunks' start states come
+    from one pass over the chunks (`pcs_gla_chunk_scan`)."""
+    H, D, V = s_pool.shape[1:]
+    dt, dev = proj.dtype, proj.device
+    plan = _gla_chunk_plan(batch, chunk)
+    nc = plan["n_chunks"]
+    f32 = dict(dtype=torch.float32, device=dev)
+    qd, kd = torch.empty(nc * H, chunk, D, **f32), torch.empty(nc * H, chunk, D, **f32)
+    g, vf, a = torch.empty(nc * H, D, **f32), torch.empty(nc * H, chunk, V, **f32), torch.empty(nc * H, chunk, chunk, **f32)
+    p = pcs_gla_chunk_params()
+    p.proj, p.row_stride = proj.data_ptr(), proj.stride(0)
+    p.q_off, p.k_off, p.v_off, p.g_off = offs
+    p.ld, p.heads, p.dim, p.vdim, p.chunk, p.q_scale, p.eps = ld.data_ptr(), H, D, V, chunk, float(D) ** -0.5, float(eps)
+    p.chunk_first, p.chunk_len, p.n_chunks, p.n_tokens, p.dtype, p.n_seqs = plan["first"].data_ptr(), plan["len"].data_ptr(), nc, batch.n_tokens, dtype_code(dt), batch.n_seqs
+    p.qd, p.kd, p.g, p.vf, p.a = qd.data_ptr(), kd.data_ptr(), g.data_ptr(), vf.data_ptr(), a.data_ptr()
+    _check(load().pcs_gla_chunk_prep(C.byref(p), _stream()), "pcs_gla_chunk_prep")
+    u = torch.bmm(kd.transpose(1, 2), vf)                  # [chunks * H, dim, vdim]: every chunk's own sum of k v^T, decayed to its end
+    p.u, p.s_pool = u.data_ptr(), s_pool.data_ptr()
+    p.seq_slot, p.seq_pos0, p.seq_chunk0, p.seq_chunks = batch.seq_slot.data_ptr(), batch.seq_pos0.data_ptr(), plan["seq0"].data_ptr(), plan["seqn"].data_ptr()
+    _check(load().pcs_gla_chunk_scan(C.byref(p), _stream()), "pcs_gla_chunk_scan")   # u now holds the state every chunk starts from
+    o = torch.baddbmm(torch.bmm(a, vf), qd, u)             # [chunks * H, chunk, vdim]
+    p.o, p.tok_row, p.norm_w, p.out = o.data_ptr(), plan["tok_row"].data_ptr(), norm_w.data_ptr(), out.data_ptr()
+    _check(load().pcs_gla_chunk_out(C.byref(p), _stream()), "pcs_gla_chunk_out")
+
+
 def gla_scan(proj: torch.Tensor, offs, ld: torch.Tensor, norm_w: torch.Tensor, out: torch.Tensor, s_pool: torch.Tensor, eps: float, batch: Batch,
              impl: int = 0) -> None:
     """proj [T, *] with q / k / v / gate columns at `offs`; ld float32 [T, H * dim] log decays; state pool float32 [slots, H, dim, vdim];
-    out [T, H * vdim]."""
+    out [T, H * vdim].  impl 0: by step (prompts in chunks, short steps token by token); 1: token by token with the state in shared
+    memory; 2: token by token (registers where the sizes allow); 3: in chunks."""
     _cuda(proj, ld, norm_w, out, s_pool)
     dt = proj.dtype
     _rows2d(proj, dt, "gla_scan: proj")
@@ -784,6 +851,9 @@ def gla_scan(proj: torch.Tensor, offs, ld: torch.Tensor, norm_w: torch.Tensor, o
     H, D, V = s_pool.shape[1:]
     if ld.dtype != torch.float32 or not ld.is_contiguous() or tuple(ld.shape) != (proj.shape[0], H * D) or norm_w.dtype != dt or norm_w.numel() != V:
         raise NativeError("gla_scan: ld float32 [T, H * dim], norm_w [vdim] in the compute type")
+    chunk_fits = 3 * GLA_CHUNK * (D + 1) * 4 <= 220 * 1024
+    if impl == 3 or (impl == 0 and batch.max_len >= GLA_CHUNK_MIN_LEN and chunk_fits and not torch.cuda.is_current_stream_capturing()):
+        return gla_scan_chunked(proj, offs, ld, norm_w, out, s_pool, eps, batch)
     p = pcs_gla_params()
     p.proj, p.row_stride = proj.data_ptr(), proj.stride(0)
     p.q_off, p.k_off, p.v_off, p.g_off = offs
@@ -791,7 +861,7 @@ def gla_scan(proj: torch.Tensor, offs, ld: torch.Tensor, norm_w: torch.Tensor, o
     p.heads, p.dim, p.vdim, p.q_scale, p.eps = H, D, V, float(D) ** -0.5, float(eps)
     p.seq_slot, p.seq_pos0, p.seq_len, p.seq_off = (batch.seq_slot.data_ptr(), batch.seq_pos0.data_ptr(), batch.seq_len.data_ptr(),
                                                     batch.seq_off.data_ptr())
-    p.n_seqs, p.n_tokens, p.dtype, p.max_len, p.impl = batch.n_seqs, batch.n_tokens, dtype_code(dt), batch.max_len, int(impl)
+    p.n_seqs, p.n_tokens, p.dtype, p.max_len, p.impl = batch.n_seqs, batch.n_tokens, dtype_code(dt), batch.max_len, 1 if impl == 1 else 0
     o_raw = torch.empty(batch.n_tokens, H * V, dtype=torch.float32, device=proj.device)
     p.o_raw = o_raw.data_ptr()
     _check(load().pcs_gla_scan(C.byref(p), _stream()), "pcs_gla_scan")

@@ -1,6 +1,7 @@
 """Throughput of the slot-pool designs beside the closest existing model at equal sizes: `bench.py --design mutolix`
-(against the Llama prompt-cache path) and `bench.py --design raritar` (against Mutolix's attention layers with a dense
-feed-forward of the same active size, which share the step function, the pool and the attention kernels).  Random weights, synthetic token ids.  Prefill and decode tokens/s of both models through their own
+(against the Llama prompt-cache path), `bench.py --design raritar` (against Mutolix's attention layers with a dense
+feed-forward of the same active size, which share the step function, the pool and the attention kernels) and
+`bench.py --design safilorn` (against Mutolix with the same order and sizes of recurrent and attention layers).  Random weights, synthetic token ids.  Prefill and decode tokens/s of both models through their own
 step / forward, then every kernel of the new design alone against its roofline, next to the like kernel of the Llama path.
 
 Timing: CUDA events on the launching stream, >= 3 warm-up iterations, a 256 MiB write between timed iterations (flushes the
@@ -380,9 +381,214 @@ def raritar_kernels(s: dict, dev, timer: Timer, prompt: int, ctx: int, hbm_gbs: 
     return out
 
 
+# ---- Safilorn ---------------------------------------------------------------------------------------------------------
+SAFILORN_SIZES = {
+    # the recurrent and attention sizes of SIZES; latent attention: per head dim plain + rot rotated key numbers, kv / q latent ranks;
+    # the feed-forward alternates dense (ff) and experts (E of eff, `top` active: the same active size)
+    "w1024": dict(SIZES["w1024"], D=96, R=32, C=256, Q=512, rank=16, tau=16.0, E=8, top=2, eff=2048),
+    "w2048": dict(SIZES["w2048"], D=96, R=32, C=512, Q=768, rank=32, tau=16.0, E=16, top=4, eff=2048),
+}
+
+
+def safilorn_config(s: dict) -> dict:
+    dense = {"kind": "dense", "ff": s["ff"]}
+    moe = {"kind": "moe", "expert": {"ff": s["eff"], "limit": 7.0}, "router": {"experts": s["E"], "top": s["top"]}}
+    att = lambda mlp: {"type": "latent_attention", "mlp": mlp,
+                       "mixer": {"heads": s["H"], "dim": s["D"], "rot_dim": s["R"], "vdim": s["V"], "kv_rank": s["C"], "q_rank": s["Q"], "scale": (s["D"] + s["R"]) ** -0.5,
+                                 "rot": {"base": 10000.0, "dims": s["R"], "scaling": {"factor": 8.0, "original": 4096, "fast": 32.0, "slow": 1.0}}}}
+    rec = lambda mlp: {"type": "gla", "mixer": {"heads": s["mH"], "dim": s["mD"], "vdim": s["mV"], "tau": s["tau"]}, "mlp": mlp}
+    return {"architecture": "Safilorn", "vocab": s["vocab"], "width": s["width"], "embedding": {"scale": 1.0}, "norm": {"eps": 1e-5},
+            "layers": [rec(dense), att(moe), att(dense), rec(moe)] * s["repeat"]}
+
+
+def safilorn_tensors(cfg: dict, s: dict, device, seed: int = 0) -> Dict[str, torch.Tensor]:
+    g = torch.Generator(device=device).manual_seed(seed)
+    W, t = cfg["width"], {}
+    rnd = lambda *shape, std=1.0, mean=0.0: (torch.randn(*shape, generator=g, device=device) * std + mean).to(torch.bfloat16)
+    lin = lambda o, i: rnd(o, i, std=i ** -0.5)
+    t["embed"], t["final.norm"], t["head"] = rnd(cfg["vocab"], W), rnd(W, std=0.05), lin(cfg["vocab"], W)
+    for i, layer in enumerate(cfg["layers"]):
+        p, m, f = f"l{i}.", layer["mixer"], layer["mlp"]
+        for n in ("norm1", "norm1b", "norm2", "norm2b"):
+            t[p + n] = rnd(W, std=0.05)
+        t[p + "dwa"] = torch.cat([rnd(i + 1, std=0.1 / (i + 1)), rnd(1, std=0.02, mean=1.0)])
+        if layer["type"] == "latent_attention":
+            H, D, R, V, C, Q = m["heads"], m["dim"], m["rot_dim"], m["vdim"], m["kv_rank"], m["q_rank"]
+            t[p + "mix.dq"], t[p + "mix.dq.norm"], t[p + "mix.uq"] = lin(Q, W), rnd(Q, std=0.05, mean=1.0), lin(H * (D + R), Q)
+            t[p + "mix.dkv"], t[p + "mix.dkv.norm"] = lin(C + R, W), rnd(C, std=0.05, mean=1.0)
+            t[p + "mix.uk"], t[p + "mix.uv"], t[p + "mix.sink"] = lin(H * D, C), lin(H * V, C), rnd(H, std=1.0)
+            t[p + "mix.g"], t[p + "mix.o"] = lin(H, W), lin(W, H * V)
+        else:
+            H, D, V = m["heads"], m["dim"], m["vdim"]
+            t[p + "mix.q"], t[p + "mix.k"], t[p + "mix.v"], t[p + "mix.g"] = lin(H * D, W), lin(H * D, W), lin(H * V, W), lin(H * V, W)
+            t[p + "mix.o"], t[p + "mix.norm"] = lin(W, H * V), rnd(V, std=0.05, mean=1.0)
+            t[p + "mix.a1"], t[p + "mix.a2"], t[p + "mix.a2.b"] = lin(s["rank"], W), lin(H * D, s["rank"]), rnd(H * D, std=1.0, mean=3.0)
+        if f["kind"] == "dense":
+            ff = f["ff"]
+            t[p + "mlp.gate"], t[p + "mlp.up"], t[p + "mlp.down"] = lin(ff, W), lin(ff, W), lin(W, ff)
+            t[p + "mlp.gate.b"], t[p + "mlp.up.b"], t[p + "mlp.down.b"] = rnd(ff, std=0.1), rnd(ff, std=0.1), rnd(W, std=0.1)
+        else:
+            E, ff = f["router"]["experts"], f["expert"]["ff"]
+            t[p + "mlp.router"], t[p + "mlp.router.b"] = rnd(E, W, std=3 * W ** -0.5), rnd(E, std=0.1)
+            for e in range(E):
+                t[f"{p}mlp.e{e}.gate"], t[f"{p}mlp.e{e}.up"], t[f"{p}mlp.e{e}.down"] = lin(ff, W), lin(ff, W), lin(W, ff)
+    return t
+
+
+def safilorn_block(s: dict, dev, timer: Timer, prompt: int, batch: int, ctx: int) -> dict:
+    from .model.mutolix import MutolixConfig, MutolixForCausalLM
+    from .model.safilorn import SafilornConfig, SafilornForCausalLM
+    cfg = safilorn_config(s)
+    out = {"layers": len(cfg["layers"]), "width": s["width"], "active_ff": s["ff"]}
+    m = SafilornForCausalLM(SafilornConfig(cfg), safilorn_tensors(cfg, s, dev), device=dev, dtype=torch.bfloat16)
+    _throughput(m, s, timer, prompt, batch, ctx, out)
+    del m
+    torch.cuda.empty_cache()
+    mc = mutolix_config(s)   # the closest existing model: recurrent and attention layers in the same order, at the same sizes
+    mm = MutolixForCausalLM(MutolixConfig(mc), random_tensors(mc, dev), device=dev, dtype=torch.bfloat16)
+    _throughput(mm, s, timer, prompt, batch, ctx, out, prefix="mutolix_")
+    del mm
+    torch.cuda.empty_cache()
+    return out
+
+
+def safilorn_kernels(s: dict, dev, timer: Timer, prompt: int, ctx: int, hbm_gbs: float, tflops: float) -> dict:
+    """Every kernel of the design alone at this size, achieved / peak, beside the like kernel of the closest model."""
+    from . import _native_seq as nsq
+    bf, H, G, D, R, V, C, Q, W = torch.bfloat16, s["H"], s["G"], s["D"], s["R"], s["V"], s["C"], s["Q"], s["width"]
+    out = {}
+    gb = lambda by, ms: {"us": round(ms * 1e3, 2), "gb_s": round(by / ms / 1e6, 1), "of_measured_hbm_peak": round(by / ms / 1e6 / hbm_gbs, 4)}
+    tf = lambda fl, ms: {"ms": round(ms, 4), "tflops": round(fl / ms / 1e9, 1), "of_measured_bf16_peak": round(fl / ms / 1e9 / tflops, 3)}
+    cap = ((max(prompt, ctx + 1) + 127) // 128) * 128
+    b, b1 = nsq.Batch([0], [0], [prompt], dev), nsq.Batch([0], [ctx], [1], dev)
+    sink = torch.randn(H, device=dev)
+    r1, r2 = torch.full((H,), 0.5, device=dev), torch.full((H,), 0.5, device=dev)
+    # prompt attention over expanded keys (every head its own rows): FLOPs = 2 (D + R + V) per (query, visible key) pair and head
+    kd, vd = torch.randn(1, H, cap, D + R, device=dev).to(bf), torch.randn(1, H, cap, V, device=dev).to(bf)
+    q, o = torch.randn(prompt, H * (D + R), device=dev).to(bf), torch.empty(prompt, H * V, device=dev, dtype=bf)
+    ids = torch.zeros(1, dtype=torch.int32, device=dev)
+    ms = timer(lambda: nsq.attention(q, kd, vd, o, H, (D + R) ** -0.5, None, None, True, b, sink_logit=sink, pool_slot=ids))
+    out["attn_prompt_expanded"] = tf(2.0 * (D + R + V) * H * prompt * (prompt + 1) / 2, ms)
+    kp, vp = torch.randn(1, G, cap, D + R, device=dev).to(bf), torch.randn(1, G, cap, V, device=dev).to(bf)
+    ms = timer(lambda: nsq.attention(q, kp, vp, o, H, (D + R) ** -0.5, r1, r2, True, b))
+    out["like_attn_prompt"] = tf(2.0 * (D + R + V) * H * prompt * (prompt + 1) / 2, ms)
+    # what the expanded form adds per layer: latents out of the pool, one product, per-head rows written (bytes: rows read and written)
+    pool = torch.randn(1, 1, cap, C + R, device=dev).to(bf)
+    wukv = (torch.randn(H * (D + V), C, device=dev) * C ** -0.5).to(bf)
+
+    def expand():
+        kv = nsq.linear(nsq.latent_gather(pool, C, b), wukv)
+        nsq.latent_expand(kv, pool, C, R, H, D, V, kd, vd, b)
+    ms = timer(expand)
+    out["latent_expand_chain"] = dict(tf(2.0 * prompt * C * H * (D + V), ms), **{"gb_s": round(prompt * (2.0 * C * 2 + 4.0 * H * (D + V) + 2.0 * H * (D + R + V)) / ms / 1e6, 1)})
+    # decoding in the latent space: every head reads the same rows, bytes = the sequence's cached rows once
+    q1, o1 = torch.randn(1, H * (C + R), device=dev).to(bf), torch.empty(1, H * C, device=dev, dtype=bf)
+    wsd = nsq.attn_workspace(1, H, C, dev)
+    ms = timer(lambda: nsq.attention(q1, pool, pool, o1, H, 0.1, None, None, True, b1, max_keys=cap, workspace=wsd, sink_logit=sink, v_row_stride=C + R), steps=15)
+    out["attn_decode_latent"] = dict(gb(2.0 * (ctx + 1) * (C + R), ms), flops_per_byte=round(2.0 * H * (2 * C + R) / (2.0 * (C + R)), 1))
+    qm, om = torch.randn(1, H * (D + R), device=dev).to(bf), torch.empty(1, H * V, device=dev, dtype=bf)
+    wsm = nsq.attn_workspace(1, H, V, dev)
+    ms = timer(lambda: nsq.attention(qm, kp, vp, om, H, 0.1, r1, r2, True, b1, max_keys=cap, workspace=wsm), steps=15)
+    out["like_attn_decode"] = gb(2.0 * G * (ctx + 1) * (D + R + V), ms)
+    # norms, rotation and append: reads the projection row, writes the query latent and one cached row
+    proj = torch.randn(prompt, Q + C + R + H, device=dev).to(bf)
+    fr = torch.tensor([10000.0 ** (-2.0 * i / R) for i in range(R // 2)], dtype=torch.float64, device=dev)
+    cq, wq_, wc_ = torch.empty(prompt, Q, device=dev, dtype=bf), torch.ones(Q, device=dev, dtype=bf), torch.ones(C, device=dev, dtype=bf)
+    ms = timer(lambda: nsq.latent_prep(proj, 0, Q, Q, C, R, wq_, wc_, 1e-5, fr, 1.2, cq, pool, b))
+    out["latent_prep"] = gb(prompt * (Q + C + R) * 4.0, ms)
+    ms = timer(lambda: nsq.latent_q(q, H, D, R, fr, 1.2, b))
+    out["latent_q_rotation"] = gb(prompt * H * R * 4.0, ms)
+    nq, nk = H * (D + R), G * (D + R + V)
+    pj = torch.randn(prompt, nq + nk, device=dev).to(bf)
+    qn, kn = torch.ones(nq, device=dev, dtype=bf), torch.ones(G * (D + R), device=dev, dtype=bf)
+    ms = timer(lambda: nsq.qk_prep(pj, (0, nq, nq + G * (D + R)), qn, kn, 1e-5, H, G, D + R, V, 0.0, 0, q, kp, vp, None, None, b))
+    out["like_qk_prep"] = gb(prompt * (nq + nk) * 4.0, ms)
+    # the depth average with the next norm: reads n results (4 B), writes the stream (4 B) and h (2 B); like: gated norm + residual + next norm
+    n_terms = 5
+    xs, h = torch.randn(n_terms + 1, prompt, W, device=dev), torch.empty(prompt, W, device=dev, dtype=bf)
+    coef, wn = torch.rand(n_terms, device=dev), torch.zeros(W, device=dev, dtype=bf)
+    ms = timer(lambda: nsq.depth_mix(xs, n_terms, coef, 1e-5, x_out=xs[n_terms], next_w=wn, h_out=h, w_offset=1.0))
+    out["depth_mix_5_terms"] = gb(prompt * W * (4.0 * n_terms + 6.0), ms)
+    x, y = xs[0], torch.randn(prompt, W, device=dev).to(bf)
+    ms = timer(lambda: nsq.gate_norm_add(x, y, None, wn, None, 1e-5, wn, h, w_offset=1.0))
+    out["norm_add_norm"] = gb(prompt * W * 12.0, ms)
+    ms = timer(lambda: nsq.gate_norm_add(x, y, y, wn, wn, 1e-5, wn, h))
+    out["like_gate_norm_add"] = gb(prompt * W * 14.0, ms)
+    # the recurrence over a prompt (sequential in the tokens) and of one decoded token (state read and written once)
+    mH, mD, mV, rk = s["mH"], s["mD"], s["mV"], s["rank"]
+    pr = (torch.randn(prompt, 2 * mH * mD + 2 * mH * mV + rk, device=dev) * 0.3).to(bf)
+    offs = (0, mH * mD, 2 * mH * mD, 2 * mH * mD + mH * mV)
+    a2, a2b = (torch.randn(mH * mD, rk, device=dev) * rk ** -0.5).to(bf), torch.full((mH * mD,), 3.0, device=dev)
+    ms = timer(lambda: nsq.gla_decay(pr[:, offs[3] + mH * mV:], a2, a2b, s["tau"]))
+    out["gla_decay"] = gb(prompt * mH * mD * 4.0, ms)
+    ld = nsq.gla_decay(pr[:, offs[3] + mH * mV:], a2, a2b, s["tau"])
+    sp, nw, og = torch.zeros(1, mH, mD, mV, device=dev), torch.ones(mV, device=dev, dtype=bf), torch.empty(prompt, mH * mV, device=dev, dtype=bf)
+    ms = timer(lambda: nsq.gla_scan(pr, offs, ld, nw, og, sp, 1e-5, b), steps=5)
+    out["gla_scan_prompt"] = {"ms": round(ms, 3), "us_per_token": round(ms * 1e3 / prompt, 3), "gflops": round(4.0 * mH * mD * mV * prompt / ms / 1e6, 1)}
+    ms = timer(lambda: nsq.gla_scan(pr[:1], offs, ld[:1], nw, og[:1], sp, 1e-5, b1), steps=15)
+    out["gla_scan_decode"] = gb(8.0 * mH * mD * mV, ms)
+    ig, fg = torch.randn(prompt, mH, device=dev), -torch.rand(prompt, mH, device=dev) * 0.1
+    npool, mp, nwm = torch.zeros(1, mH, mD, device=dev), torch.zeros(1, mH, device=dev), torch.ones(mH * mV, device=dev, dtype=bf)
+    ms = timer(lambda: nsq.mlstm_scan(pr, offs, ig, fg, nwm, og, sp, npool, mp, 1e-5, b), steps=5)
+    out["like_mlstm_scan_prompt"] = {"ms": round(ms, 3), "us_per_token": round(ms * 1e3 / prompt, 3), "gflops": round(4.0 * mH * mD * mV * prompt / ms / 1e6, 1)}
+    ms = timer(lambda: nsq.mlstm_scan(pr, offs, ig, fg, nwm, og, sp, npool, mp, 1e-5, b, impl=2), steps=5)
+    out["like_mlstm_scan_prompt_token_by_token"] = {"ms": round(ms, 3), "us_per_token": round(ms * 1e3 / prompt, 3)}
+    ms = timer(lambda: nsq.mlstm_scan(pr[:1], offs, ig[:1], fg[:1], nwm, og[:1], sp, npool, mp, 1e-5, b1), steps=15)
+    out["like_mlstm_scan_decode"] = gb(8.0 * mH * mD * mV, ms)
+    # router and experts
+    E, top, ff = s["E"], s["top"], s["eff"]
+    hb = torch.randn(prompt, W, device=dev).to(bf)
+    wr, br = (torch.randn(E, W, device=dev) * 3 * W ** -0.5).to(bf), torch.zeros(E, device=dev)
+    ms = timer(lambda: nsq.moe_route(hb, wr, None, None, top, bias=br, renorm=True))
+    out["moe_route"] = gb(prompt * W * 2.0, ms)
+    idx, wgt, _ = nsq.moe_route(hb, wr, None, None, top, bias=br, renorm=True)
+    act = (nsq.GLU_CLAMPED_SWISH, 1.702, 7.0)
+    wgu, wdn = (torch.randn(E, 2 * ff, W, device=dev) * W ** -0.5).to(bf), (torch.randn(E, W, ff, device=dev) * ff ** -0.5).to(bf)
+    pairs = prompt * top
+    ms = timer(lambda: nsq.moe_experts(hb, idx, wgu, wdn, grouped="library", act=act))
+    out["moe_experts_prompt"] = dict(tf(6.0 * ff * W * pairs, ms), what="plan + gather + library grouped products + clamped swish")
+    xa = torch.randn(pairs, W, device=dev).to(bf)
+    ms = timer(lambda: torch.nn.functional.linear(torch.nn.functional.linear(xa, wgu[0])[:, :ff], wdn[0]))
+    out["like_dense_ff_products"] = tf(6.0 * ff * W * pairs, ms)
+    i1 = idx[:1].contiguous()
+    ms = timer(lambda: nsq.moe_experts(hb[:1], i1, wgu, wdn, grouped=False, act=act), steps=15)
+    out["moe_experts_decode"] = gb(top * 3.0 * ff * W * 2, ms)
+    wl = (torch.randn(top * 3 * ff, W, device=dev) * W ** -0.5).to(bf)
+    ms = timer(lambda: nsq.linear(hb[:1], wl, kernel=True), steps=15)
+    out["like_linear_rows"] = gb(top * 3.0 * ff * W * 2, ms)
+    return out
+
+
+def run_safilorn(args, load_peaks, ClockSampler) -> None:
+    from . import _native_seq as nsq
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    nsq.load()
+    hbm, kind, tfl = load_peaks()
+    timer = Timer(dev)
+    sampler = ClockSampler(0)
+    sampler.start()
+    sampler.mark()
+    before = nsq.launch_count()
+    line = {"design": "safilorn", "compared_with": "mutolix (recurrent and attention layers in the same order, at the same sizes) on the same step function, "
+                                                   "pool and kernels",
+            "dtype": "bf16", "data": "synthetic", "peaks": {"hbm_gbs": hbm, "bf16_tflops": tfl, "kind": kind},
+            "timing": "CUDA events, 3 warm-up iterations, 256 MiB L2 flush between iterations, median", "sizes": {}}
+    prompt, batch, ctx = 2048, 4, 2048
+    for name, s in SAFILORN_SIZES.items():
+        blk = safilorn_block(s, dev, timer, prompt, batch, ctx)
+        blk["kernels"] = safilorn_kernels(s, dev, timer, prompt, ctx, hbm, tfl)
+        line["sizes"][name] = blk
+    line["gpu_launches"] = nsq.launch_count() - before
+    line["clocks"] = sampler.stop()
+    print(json.dumps(line), flush=True)
+
+
 def run(args, load_peaks, ClockSampler) -> None:
     if args.design == "raritar":
         return run_raritar(args, load_peaks, ClockSampler)
+    if args.design == "safilorn":
+        return run_safilorn(args, load_peaks, ClockSampler)
     from . import _native as nat, _native_seq as nsq, build as pc_build
     dev = torch.device("cuda", 0)
     torch.cuda.set_device(dev)

@@ -32,6 +32,38 @@ __global__ void __launch_bounds__(256) gla_decay_kernel(const T* __restrict__ a,
   }
 }
 
+// Many tokens: block = (256 channels, kDecayTokens tokens).  The block's rows of A2 sit in shared memory transposed (a thread reads
+// its own channel's numbers without bank conflicts) and the tokens' low-rank inputs beside them (broadcast reads); a thread
+// owns one channel and walks the tokens, so the stores of a token are contiguous over the threads.  The sum runs over r in
+// increasing order as in the kernel above: both give the same bits.
+constexpr int kDecayTokens = 32;
+template <typename T>
+__global__ void __launch_bounds__(256) gla_decay_tile_kernel(const T* __restrict__ a, long long a_stride, const T* __restrict__ a2,
+                                                             const float* __restrict__ a2_b, float* __restrict__ ld, int n_tokens, int n_channels,
+                                                             int rank, float inv_tau) {
+  extern __shared__ float sm[];
+  float* w = sm;                 // [rank][256]
+  float* as = sm + rank * 256;   // [kDecayTokens][rank]
+  const int c = blockIdx.x * 256 + threadIdx.x, t0 = blockIdx.y * kDecayTokens;
+  const int nt = min(kDecayTokens, n_tokens - t0);
+  for (int e = threadIdx.x; e < 256 * rank; e += 256) {
+    const int cc = e / rank, r = e - cc * rank, ch = blockIdx.x * 256 + cc;
+    w[r * 256 + cc] = ch < n_channels ? ldf(a2 + static_cast<long long>(ch) * rank + r) : 0.f;
+  }
+  for (int e = threadIdx.x; e < nt * rank; e += 256) {
+    const int i = e / rank, r = e - i * rank;
+    as[e] = ldf(a + static_cast<long long>(t0 + i) * a_stride + r);
+  }
+  __syncthreads();
+  if (c >= n_channels) return;
+  const float bias = a2_b ? a2_b[c] : 0.f;
+  for (int i = 0; i < nt; ++i) {
+    float z = 0.f;
+    for (int r = 0; r < rank; ++r) z = fmaf(w[r * 256 + threadIdx.x], as[i * rank + r], z);
+    ld[static_cast<long long>(t0 + i) * n_channels + c] = logsigmoidf_(z + bias) * inv_tau;
+  }
+}
+
 // Grid (sequence, head, slice of value columns): the columns of S evolve independently given the decays, k and q.  Thread
 // (r, c) owns rows r, r + R, ... of column c of the slice; threads past VS * R only take part in loads.
 template <typename T>
@@ -258,13 +290,180 @@ __global__ void __launch_bounds__(256) gla_out_kernel(const pcs_gla_params p) {
   }
 }
 
+// ---- the chunkwise form (prompts) -------------------------------------------------------------------------------------
+// One block per (chunk, head).  q, k and the running sums of the log decays of the chunk sit in shared memory as 32-bit rows
+// of dim + 1 numbers (a row per token: threads that walk the tokens at a fixed channel touch different banks).  The scores
+// inside the chunk are formed pair by pair with the exact factor exp(B_i[d] - B_s[d]) <= 1 per channel, so no decay, however
+// strong, overflows a factor; everything that crosses chunks is left to matrix products on exp(B_i) and exp(B_e - B_i) <= 1.
+template <typename T>
+__global__ void __launch_bounds__(256) gla_chunk_prep_kernel(const pcs_gla_chunk_params p) {
+  extern __shared__ float sm[];
+  const int D = p.dim, V = p.vdim, H = p.heads, C = p.chunk, DP = D + 1;
+  float* qs = sm;              // [C][DP]
+  float* ks = qs + C * DP;     // [C][DP]
+  float* Bs = ks + C * DP;     // [C][DP]
+  const int cn = blockIdx.x, head = blockIdx.y, tid = threadIdx.x;
+  const int first = p.chunk_first[cn], n = p.chunk_len[cn];
+  const T* proj = static_cast<const T*>(p.proj);
+  for (int e = tid; e < C * D; e += 256) {
+    const int i = e / D, d = e - i * D;
+    float qv = 0.f, kv = 0.f, lv = 0.f;
+    if (i < n) {
+      const T* row = proj + static_cast<long long>(first + i) * p.row_stride;
+      qv = ldf(row + p.q_off + head * D + d) * p.q_scale;
+      kv = ldf(row + p.k_off + head * D + d);
+      lv = p.ld[static_cast<long long>(first + i) * (H * D) + head * D + d];
+    }
+    qs[i * DP + d] = qv;
+    ks[i * DP + d] = kv;
+    Bs[i * DP + d] = lv;
+  }
+  __syncthreads();
+  for (int d = tid; d < D; d += 256) {  // running sums over the chunk's tokens, per channel (rows past the chunk add nothing)
+    float acc = 0.f;
+    for (int i = 0; i < C; ++i) {
+      acc += Bs[i * DP + d];
+      Bs[i * DP + d] = acc;
+    }
+  }
+  __syncthreads();
+  const long long base = static_cast<long long>(cn) * H + head;
+  float* qd = p.qd + base * C * D;
+  float* kd = p.kd + base * C * D;
+  const float* Be = Bs + (C - 1) * DP;
+  for (int e = tid; e < C * D; e += 256) {
+    const int i = e / D, d = e - i * D;
+    const float bi = Bs[i * DP + d];
+    qd[e] = qs[i * DP + d] * expf(bi);
+    kd[e] = ks[i * DP + d] * expf(Be[d] - bi);
+  }
+  for (int d = tid; d < D; d += 256) p.g[base * D + d] = expf(Be[d]);
+  float* vf = p.vf + base * C * V;
+  for (int e = tid; e < C * V; e += 256) {
+    const int i = e / V, c = e - i * V;
+    vf[e] = i < n ? ldf(proj + static_cast<long long>(first + i) * p.row_stride + p.v_off + head * V + c) : 0.f;
+  }
+  // scores inside the chunk: lanes walk the keys s of one query i (k and B rows in different banks, q and B_i broadcast)
+  float* a = p.a + base * C * C;
+  for (int e = tid; e < C * C; e += 256) {
+    const int i = e / C, s_ = e - i * C;
+    float acc = 0.f;
+    if (s_ <= i && i < n) {
+      const float* qi = qs + i * DP;
+      const float* bi = Bs + i * DP;
+      const float* kk = ks + s_ * DP;
+      const float* bs = Bs + s_ * DP;
+      float a0 = 0.f, a1 = 0.f;
+      int d = 0;
+      for (; d + 1 < D; d += 2) {
+        a0 = fmaf(qi[d] * kk[d], expf(bi[d] - bs[d]), a0);
+        a1 = fmaf(qi[d + 1] * kk[d + 1], expf(bi[d + 1] - bs[d + 1]), a1);
+      }
+      if (d < D) a0 = fmaf(qi[d] * kk[d], expf(bi[d] - bs[d]), a0);
+      acc = a0 + a1;
+    }
+    a[e] = acc;
+  }
+}
+
+// One thread per element of the state (4 neighbouring value columns where vdim allows): the entry's chunks in order.
+__global__ void __launch_bounds__(256) gla_chunk_scan_kernel(const pcs_gla_chunk_params p) {
+  const int D = p.dim, V = p.vdim, H = p.heads;
+  const int b = blockIdx.z, head = blockIdx.y;
+  const int nchunks = p.seq_chunks[b];
+  if (nchunks <= 0) return;
+  const long long e = (static_cast<long long>(blockIdx.x) * 256 + threadIdx.x);
+  if (e >= static_cast<long long>(D) * V) return;
+  const int d = static_cast<int>(e / V);
+  const int slot = p.seq_slot[b], c0 = p.seq_chunk0[b];
+  float* Sg = p.s_pool + (static_cast<long long>(slot) * H + head) * D * V + e;
+  float S = p.seq_pos0[b] == 0 ? 0.f : *Sg;
+  for (int c = c0; c < c0 + nchunks; ++c) {
+    const long long base = static_cast<long long>(c) * H + head;
+    float* u = p.u + base * D * V + e;
+    const float un = *u;
+    *u = S;
+    S = fmaf(p.g[base * D + d], S, un);
+  }
+  *Sg = S;
+}
+
+template <typename T>
+__global__ void __launch_bounds__(256) gla_chunk_out_kernel(const pcs_gla_chunk_params p) {
+  const int V = p.vdim, H = p.heads, C = p.chunk, lane = threadIdx.x & 31;
+  const long long item = static_cast<long long>(blockIdx.x) * 8 + (threadIdx.x >> 5);
+  if (item >= static_cast<long long>(p.n_tokens) * H) return;
+  const long long t = item / H;
+  const int head = static_cast<int>(item - t * H);
+  const int row = p.tok_row[t];
+  const float* o = p.o + ((static_cast<long long>(row / C) * H + head) * C + row % C) * V;
+  const T* g = static_cast<const T*>(p.proj) + t * p.row_stride + p.g_off + head * V;
+  const T* nw = static_cast<const T*>(p.norm_w);
+  float ss = 0.f;
+  for (int c = lane; c < V; c += 32) ss = fmaf(o[c], o[c], ss);
+  ss = warp_sum(ss);
+  const float inv = 1.f / sqrtf(ss / static_cast<float>(V) + p.eps);
+  T* out = static_cast<T*>(p.out) + t * (static_cast<long long>(H) * V) + head * V;
+  for (int c = lane; c < V; c += 32) {
+    const float gv = ldf(g + c);
+    stf(out + c, o[c] * inv * ldf(nw + c) * (gv * sigmoidf_(gv)));
+  }
+}
+
 }  // namespace pcs
+
+PCS_API int pcs_gla_chunk_prep(const pcs_gla_chunk_params* p, void* stream) {
+  PCS_REQUIRE(p, "pcs_gla_chunk_prep: null params");
+  if (p->n_chunks == 0) return PCS_OK;
+  PCS_REQUIRE(p->proj && p->ld && p->chunk_first && p->chunk_len && p->qd && p->kd && p->g && p->vf && p->a, "pcs_gla_chunk_prep: null tensor");
+  PCS_REQUIRE(p->heads > 0 && p->heads <= 65535 && p->dim > 0 && p->vdim > 0 && p->chunk > 0, "pcs_gla_chunk_prep: bad sizes");
+  const size_t smem = static_cast<size_t>(3) * p->chunk * (p->dim + 1) * sizeof(float);
+  PCS_REQUIRE(smem <= 220 * 1024, "pcs_gla_chunk_prep: a chunk of %d tokens x %d channels exceeds shared memory", p->chunk, p->dim);
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (smem > 48 * 1024)
+    PCS_DISPATCH(p->dtype, PCS_CHECK_CUDA(cudaFuncSetAttribute(pcs::gla_chunk_prep_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, 220 * 1024)));
+  PCS_DISPATCH(p->dtype, pcs::gla_chunk_prep_kernel<T><<<dim3(p->n_chunks, p->heads), 256, smem, st>>>(*p));
+  PCS_CHECK_CUDA(cudaGetLastError());
+  pcs::count_launch();
+  return PCS_OK;
+}
+
+PCS_API int pcs_gla_chunk_scan(const pcs_gla_chunk_params* p, void* stream) {
+  PCS_REQUIRE(p, "pcs_gla_chunk_scan: null params");
+  if (p->n_seqs == 0 || p->n_chunks == 0) return PCS_OK;
+  PCS_REQUIRE(p->u && p->g && p->s_pool && p->seq_slot && p->seq_pos0 && p->seq_chunk0 && p->seq_chunks, "pcs_gla_chunk_scan: null tensor");
+  PCS_REQUIRE(p->heads > 0 && p->heads <= 65535 && p->n_seqs <= 65535 && p->dim > 0 && p->vdim > 0, "pcs_gla_chunk_scan: bad sizes");
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const long long elems = static_cast<long long>(p->dim) * p->vdim;
+  pcs::gla_chunk_scan_kernel<<<dim3(static_cast<unsigned>((elems + 255) / 256), p->heads, p->n_seqs), 256, 0, st>>>(*p);
+  PCS_CHECK_CUDA(cudaGetLastError());
+  pcs::count_launch();
+  return PCS_OK;
+}
+
+PCS_API int pcs_gla_chunk_out(const pcs_gla_chunk_params* p, void* stream) {
+  PCS_REQUIRE(p, "pcs_gla_chunk_out: null params");
+  if (p->n_tokens == 0) return PCS_OK;
+  PCS_REQUIRE(p->proj && p->o && p->tok_row && p->norm_w && p->out && p->chunk > 0 && p->heads > 0 && p->vdim > 0, "pcs_gla_chunk_out: bad arguments");
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const long long items = static_cast<long long>(p->n_tokens) * p->heads;
+  PCS_DISPATCH(p->dtype, pcs::gla_chunk_out_kernel<T><<<static_cast<unsigned>((items + 7) / 8), 256, 0, st>>>(*p));
+  PCS_CHECK_CUDA(cudaGetLastError());
+  pcs::count_launch();
+  return PCS_OK;
+}
 
 PCS_API int pcs_gla_decay(const void* a, int64_t a_stride, const void* a2, const float* a2_b, float* ld, int n_tokens, int n_channels, int rank,
                           float tau, int dtype, void* stream) {
   if (n_tokens == 0) return PCS_OK;
   PCS_REQUIRE(a && a2 && ld && n_channels > 0 && rank > 0 && rank <= 8192 && tau > 0.f, "pcs_gla_decay: bad arguments");
   cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const size_t tile_smem = static_cast<size_t>(rank) * (256 + pcs::kDecayTokens) * sizeof(float);
+  if (n_tokens >= 2 * pcs::kDecayTokens && tile_smem <= 48 * 1024) {
+    dim3 grid((n_channels + 255) / 256, (n_tokens + pcs::kDecayTokens - 1) / pcs::kDecayTokens);
+    PCS_DISPATCH(dtype, pcs::gla_decay_tile_kernel<T><<<grid, 256, tile_smem, st>>>(static_cast<const T*>(a), a_stride, static_cast<const T*>(a2), a2_b, ld,
+                                                                                   n_tokens, n_channels, rank, 1.f / tau));
+  } else
   PCS_DISPATCH(dtype, pcs::gla_decay_kernel<T><<<n_tokens, 256, rank * sizeof(float), st>>>(static_cast<const T*>(a), a_stride, static_cast<const T*>(a2),
                                                                                            a2_b, ld, n_channels, rank, 1.f / tau));
   PCS_CHECK_CUDA(cudaGetLastError());

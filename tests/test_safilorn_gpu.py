@@ -239,9 +239,9 @@ def test_head_gate(nsq):
                                                 (F32, 1, 260, 16, 4, 16.0)])
 def test_gated_linear_attention_in_portions(nsq, dtype, H, D, V, r, tau):
     """The decays and the recurrence against the oracle: a prompt at once, in portions down to one token, two entries in a batch,
-    the state carried in the pool; both kernels (state in registers / in shared memory)."""
+    the state carried in the pool; token by token (state in registers / in shared memory) and in chunks of 64 tokens."""
     g = torch.Generator().manual_seed(D + V)
-    T = 50
+    T = 150
     rq = lambda *s, sc=1.0: (torch.randn(*s, generator=g, dtype=F64) * sc).to(dtype).to(F64)
     proj = rq(T, 2 * H * D + 2 * H * V + r + 8, sc=0.6)
     offs, a_off = (0, H * D, 2 * H * D, 2 * H * D + H * V), 2 * H * D + 2 * H * V + 8
@@ -257,8 +257,10 @@ def test_gated_linear_attention_in_portions(nsq, dtype, H, D, V, r, tau):
     want = O.norm_plain(o, nw, 1e-5).reshape(T, H * V) * O.silu(gate)
     tol = 2e-5 if dtype == F32 else 1.2e-2
     pd = dev(proj, dtype)
-    for impl in (0, 1):
-        for cuts in ([T], [1] * T, [17, 2, 1, 30], [2] * 25):
+    for impl in (0, 1, 2, 3):
+        for cuts in ([T], [1] * T, [17, 2, 1, 130], [2] * 75, [10, 140], [64, 64, 22], [63, 65, 22]):
+            if impl in (1, 3) and len(cuts) > 10:
+                continue
             pool = torch.full((3, H, D, V), 9.0, device=DEV)   # a slot that was used before: a first token starts from zero all the same
             out, p0 = torch.empty(T, H * V, device=DEV, dtype=dtype), 0
             for n in cuts:
@@ -268,12 +270,13 @@ def test_gated_linear_attention_in_portions(nsq, dtype, H, D, V, r, tau):
     # two entries of unequal length in one launch, the second continuing from a state
     pool = torch.zeros(4, H, D, V, device=DEV)
     out = torch.empty(T, H * V, device=DEV, dtype=dtype)
-    nsq.gla_scan(pd[:20], offs, ld[:20], dev(nw, dtype), out[:20], pool, 1e-5, batch_of(nsq, [3], [0], [20]))
-    cat = torch.cat([pd[:7], pd[20:]])
-    out2 = torch.empty(37, H * V, device=DEV, dtype=dtype)
-    nsq.gla_scan(cat, offs, torch.cat([ld[:7], ld[20:]]), dev(nw, dtype), out2, pool, 1e-5, batch_of(nsq, [0, 3], [0, 20], [7, 30]))
-    close(out2[:7], want[:7], tol, "a fresh entry beside a continued one")
-    close(out2[7:], want[20:], tol, "the continued entry")
+    for impl in (2, 3):
+        nsq.gla_scan(pd[:20], offs, ld[:20], dev(nw, dtype), out[:20], pool, 1e-5, batch_of(nsq, [3], [0], [20]), impl=impl)
+        cat = torch.cat([pd[:7], pd[20:]])
+        out2 = torch.empty(7 + T - 20, H * V, device=DEV, dtype=dtype)
+        nsq.gla_scan(cat, offs, torch.cat([ld[:7], ld[20:]]), dev(nw, dtype), out2, pool, 1e-5, batch_of(nsq, [0, 3], [0, 20], [7, T - 20]), impl=impl)
+        close(out2[:7], want[:7], tol, f"a fresh entry beside a continued one (impl {impl})")
+        close(out2[7:], want[20:], tol, f"the continued entry (impl {impl})")
 
 
 def test_decay_separates_channels(nsq):
@@ -288,11 +291,13 @@ def test_decay_separates_channels(nsq):
     ld[1:, 0], ld[1:, 1] = -50.0, -1e-4                 # channel 0 forgets, channel 1 keeps
     pool = torch.zeros(1, H, D, V, device=DEV)
     out = torch.empty(T, V, device=DEV)
-    nsq.gla_scan(dev(proj), (0, D, 2 * D, 2 * D + V), dev(ld), torch.ones(V, device=DEV), out, pool, 0.0, batch_of(nsq, [0], [0], [T]))
     o = O.gla_recurrence(proj[:, :D].view(T, 1, D) * 0.5, proj[:, D:2 * D].view(T, 1, D), proj[:, 2 * D:2 * D + V].view(T, 1, V), torch.exp(ld).view(T, 1, D))
-    close(out, O.norm_plain(o, torch.ones(V, dtype=F64), 0.0).reshape(T, V) * O.silu(proj[:, 2 * D + V:]), 1e-5, "two channels")
-    s = pool[0, 0].cpu().to(F64)
-    assert float(s[0].abs().max()) < 1e-30 and abs(float(s[1, 3]) - 4.0 * math.exp(-29e-4)) < 1e-4 and float(s[2:].abs().max()) == 0.0
+    for impl in (2, 3):   # token by token, and in chunks (a decay of e^-50 per token must not overflow any factor)
+        pool.zero_()
+        nsq.gla_scan(dev(proj), (0, D, 2 * D, 2 * D + V), dev(ld), torch.ones(V, device=DEV), out, pool, 0.0, batch_of(nsq, [0], [0], [T]), impl=impl)
+        close(out, O.norm_plain(o, torch.ones(V, dtype=F64), 0.0).reshape(T, V) * O.silu(proj[:, 2 * D + V:]), 1e-5, f"two channels (impl {impl})")
+        s = pool[0, 0].cpu().to(F64)
+        assert float(s[0].abs().max()) < 1e-30 and abs(float(s[1, 3]) - 4.0 * math.exp(-29e-4)) < 1e-4 and float(s[2:].abs().max()) == 0.0
 
 
 @pytest.mark.parametrize("E,top,T,W", [(5, 2, 9, 40), (12, 3, 70, 64), (1, 1, 4, 24), (7, 7, 5, 36), (300, 4, 6, 32)])
