@@ -404,30 +404,44 @@ __global__ void __launch_bounds__(kAttnThreads) attn_decode_kernel(const pcs_att
   }
 }
 
+constexpr int kAttnMaxSplits = 32;
+
+// Merge of the splits' partial results.  The splits' maxima and sums are read by one thread each, the common maximum, the total
+// and every split's factor exp(m_s - M) are formed once in shared memory, and the columns then need independent loads only.
 template <typename T>
 __global__ void __launch_bounds__(kAttnThreads) attn_combine_kernel(const pcs_attn_params p, int S) {
+  __shared__ float ms[kAttnMaxSplits], ls[kAttnMaxSplits], fs[kAttnMaxSplits];
+  __shared__ float inv_s;
   const int t = blockIdx.x, h = blockIdx.y, V = p.vdim;
   const float* part = p.workspace + (static_cast<long long>(t) * p.n_heads + h) * S * (V + 2);
-  float M = -INFINITY;
-  for (int s = 0; s < S; ++s) M = fmaxf(M, part[s * (V + 2)]);
-  float L = 0.f;
-  for (int s = 0; s < S; ++s) {
-    const float ms = part[s * (V + 2)];
-    if (ms != -INFINITY) L += part[s * (V + 2) + 1] * expf(ms - M);
+  if (threadIdx.x < S) {
+    ms[threadIdx.x] = part[threadIdx.x * (V + 2)];
+    ls[threadIdx.x] = part[threadIdx.x * (V + 2) + 1];
   }
-  const float inv = L > 0.f ? 1.f / L : 0.f;
+  __syncthreads();
+  if (threadIdx.x == 0) {  // the same order of sums as ever: s = 0, 1, ...
+    float M = -INFINITY;
+    for (int s = 0; s < S; ++s) M = fmaxf(M, ms[s]);
+    float L = 0.f;
+    for (int s = 0; s < S; ++s) {
+      const float f = ms[s] != -INFINITY ? expf(ms[s] - M) : 0.f;
+      fs[s] = f;
+      if (ms[s] != -INFINITY) L += ls[s] * f;
+    }
+    inv_s = L > 0.f ? 1.f / L : 0.f;
+  }
+  __syncthreads();
+  const float inv = inv_s;
   T* o = static_cast<T*>(p.out) + (static_cast<long long>(t) * p.n_heads + h) * V;
   for (int c = threadIdx.x; c < V; c += blockDim.x) {
     float a = 0.f;
-    for (int s = 0; s < S; ++s) {
-      const float ms = part[s * (V + 2)];
-      if (ms != -INFINITY) a = fmaf(part[s * (V + 2) + 2 + c], expf(ms - M), a);
-    }
+#pragma unroll 4
+    for (int s = 0; s < S; ++s) a = fmaf(part[s * (V + 2) + 2 + c], fs[s], a);
     stf(o + c, a * inv);
   }
 }
 
-constexpr int kAttnMaxSplits = 32;
+
 
 }  // namespace pcs
 

@@ -23,7 +23,7 @@ __global__ void __launch_bounds__(256) gla_decay_kernel(const T* __restrict__ a,
   const long long t = blockIdx.x;
   for (int r = threadIdx.x; r < rank; r += blockDim.x) as[r] = ldf(a + t * a_stride + r);
   __syncthreads();
-  for (int c = threadIdx.x; c < n_channels; c += blockDim.x) {
+  for (int c = blockIdx.y * blockDim.x + threadIdx.x; c < n_channels; c += gridDim.y * blockDim.x) {
     const T* w = a2 + static_cast<long long>(c) * rank;
     float z = 0.f;
     for (int r = 0; r < rank; ++r) z = fmaf(ldf(w + r), as[r], z);
@@ -295,8 +295,9 @@ __global__ void __launch_bounds__(256) gla_out_kernel(const pcs_gla_params p) {
 // of dim + 1 numbers (a row per token: threads that walk the tokens at a fixed channel touch different banks).  The scores
 // inside the chunk are formed pair by pair with the exact factor exp(B_i[d] - B_s[d]) <= 1 per channel, so no decay, however
 // strong, overflows a factor; everything that crosses chunks is left to matrix products on exp(B_i) and exp(B_e - B_i) <= 1.
+constexpr int kPrepThreads = 1024;
 template <typename T>
-__global__ void __launch_bounds__(256) gla_chunk_prep_kernel(const pcs_gla_chunk_params p) {
+__global__ void __launch_bounds__(kPrepThreads) gla_chunk_prep_kernel(const pcs_gla_chunk_params p) {
   extern __shared__ float sm[];
   const int D = p.dim, V = p.vdim, H = p.heads, C = p.chunk, DP = D + 1;
   float* qs = sm;              // [C][DP]
@@ -305,7 +306,7 @@ __global__ void __launch_bounds__(256) gla_chunk_prep_kernel(const pcs_gla_chunk
   const int cn = blockIdx.x, head = blockIdx.y, tid = threadIdx.x;
   const int first = p.chunk_first[cn], n = p.chunk_len[cn];
   const T* proj = static_cast<const T*>(p.proj);
-  for (int e = tid; e < C * D; e += 256) {
+  for (int e = tid; e < C * D; e += kPrepThreads) {
     const int i = e / D, d = e - i * D;
     float qv = 0.f, kv = 0.f, lv = 0.f;
     if (i < n) {
@@ -319,7 +320,7 @@ __global__ void __launch_bounds__(256) gla_chunk_prep_kernel(const pcs_gla_chunk
     Bs[i * DP + d] = lv;
   }
   __syncthreads();
-  for (int d = tid; d < D; d += 256) {  // running sums over the chunk's tokens, per channel (rows past the chunk add nothing)
+  for (int d = tid; d < D; d += kPrepThreads) {  // running sums over the chunk's tokens, per channel (rows past the chunk add nothing)
     float acc = 0.f;
     for (int i = 0; i < C; ++i) {
       acc += Bs[i * DP + d];
@@ -331,61 +332,92 @@ __global__ void __launch_bounds__(256) gla_chunk_prep_kernel(const pcs_gla_chunk
   float* qd = p.qd + base * C * D;
   float* kd = p.kd + base * C * D;
   const float* Be = Bs + (C - 1) * DP;
-  for (int e = tid; e < C * D; e += 256) {
+  for (int e = tid; e < C * D; e += kPrepThreads) {
     const int i = e / D, d = e - i * D;
     const float bi = Bs[i * DP + d];
     qd[e] = qs[i * DP + d] * expf(bi);
     kd[e] = ks[i * DP + d] * expf(Be[d] - bi);
   }
-  for (int d = tid; d < D; d += 256) p.g[base * D + d] = expf(Be[d]);
+  for (int d = tid; d < D; d += kPrepThreads) p.g[base * D + d] = expf(Be[d]);
   float* vf = p.vf + base * C * V;
-  for (int e = tid; e < C * V; e += 256) {
+  for (int e = tid; e < C * V; e += kPrepThreads) {
     const int i = e / V, c = e - i * V;
     vf[e] = i < n ? ldf(proj + static_cast<long long>(first + i) * p.row_stride + p.v_off + head * V + c) : 0.f;
   }
-  // scores inside the chunk: lanes walk the keys s of one query i (k and B rows in different banks, q and B_i broadcast)
+  // scores inside the chunk.  Query rows i and C - 1 - i together have C + 1 visible keys, so the pairs are walked as C / 2 rows of
+  // C + 1 places with every lane busy; lanes of a warp mostly walk the keys of one query (k and B rows in different banks, q and
+  // B_i broadcast).  Pairs above the diagonal, and rows past the chunk's end, are zero.
   float* a = p.a + base * C * C;
-  for (int e = tid; e < C * C; e += 256) {
-    const int i = e / C, s_ = e - i * C;
-    float acc = 0.f;
-    if (s_ <= i && i < n) {
-      const float* qi = qs + i * DP;
-      const float* bi = Bs + i * DP;
-      const float* kk = ks + s_ * DP;
-      const float* bs = Bs + s_ * DP;
-      float a0 = 0.f, a1 = 0.f;
-      int d = 0;
-      for (; d + 1 < D; d += 2) {
-        a0 = fmaf(qi[d] * kk[d], expf(bi[d] - bs[d]), a0);
-        a1 = fmaf(qi[d + 1] * kk[d + 1], expf(bi[d + 1] - bs[d + 1]), a1);
-      }
-      if (d < D) a0 = fmaf(qi[d] * kk[d], expf(bi[d] - bs[d]), a0);
-      acc = a0 + a1;
+  for (int e = tid; e < C * C; e += kPrepThreads) a[e] = 0.f;
+  __syncthreads();
+  const int half = (C + 1) / 2;
+  for (int e = tid; e < half * (C + 1); e += kPrepThreads) {
+    const int r = e / (C + 1), j = e - r * (C + 1);
+    int i, s_;
+    if (j <= r) { i = r; s_ = j; } else { i = C - 1 - r; s_ = j - r - 1; }
+    if (i >= n || s_ > i || (i == r && j > r)) continue;   // (an odd chunk's middle row is taken once)
+    const float* qi = qs + i * DP;
+    const float* bi = Bs + i * DP;
+    const float* kk = ks + s_ * DP;
+    const float* bs = Bs + s_ * DP;
+    float a0 = 0.f, a1 = 0.f;
+    int d = 0;
+    for (; d + 1 < D; d += 2) {
+      a0 = fmaf(qi[d] * kk[d], expf(bi[d] - bs[d]), a0);
+      a1 = fmaf(qi[d + 1] * kk[d + 1], expf(bi[d + 1] - bs[d + 1]), a1);
     }
-    a[e] = acc;
+    if (d < D) a0 = fmaf(qi[d] * kk[d], expf(bi[d] - bs[d]), a0);
+    a[i * C + s_] = a0 + a1;
   }
 }
 
-// One thread per element of the state (4 neighbouring value columns where vdim allows): the entry's chunks in order.
+// One thread per VW neighbouring value columns of one state row: the entry's chunks in order.  The sums and decays of four
+// chunks are requested before the dependent chain S <- g S + u runs over them, so four loads per thread are in flight.
+template <int VW>
 __global__ void __launch_bounds__(256) gla_chunk_scan_kernel(const pcs_gla_chunk_params p) {
   const int D = p.dim, V = p.vdim, H = p.heads;
   const int b = blockIdx.z, head = blockIdx.y;
   const int nchunks = p.seq_chunks[b];
   if (nchunks <= 0) return;
-  const long long e = (static_cast<long long>(blockIdx.x) * 256 + threadIdx.x);
+  const long long e = (static_cast<long long>(blockIdx.x) * 256 + threadIdx.x) * VW;
   if (e >= static_cast<long long>(D) * V) return;
   const int d = static_cast<int>(e / V);
   const int slot = p.seq_slot[b], c0 = p.seq_chunk0[b];
   float* Sg = p.s_pool + (static_cast<long long>(slot) * H + head) * D * V + e;
-  float S = p.seq_pos0[b] == 0 ? 0.f : *Sg;
-  for (int c = c0; c < c0 + nchunks; ++c) {
-    const long long base = static_cast<long long>(c) * H + head;
-    float* u = p.u + base * D * V + e;
-    const float un = *u;
-    *u = S;
-    S = fmaf(p.g[base * D + d], S, un);
+  float S[VW];
+#pragma unroll
+  for (int j = 0; j < VW; ++j) S[j] = p.seq_pos0[b] == 0 ? 0.f : Sg[j];
+  const long long cstride = static_cast<long long>(H) * D * V;
+  float* u0 = p.u + (static_cast<long long>(c0) * H + head) * D * V + e;
+  const float* g0 = p.g + (static_cast<long long>(c0) * H + head) * D + d;
+  constexpr int U = 4;
+  for (int c = 0; c < nchunks; c += U) {
+    float un[U][VW], gn[U];
+#pragma unroll
+    for (int k = 0; k < U; ++k) {
+      if (c + k < nchunks) {
+        gn[k] = g0[static_cast<long long>(c + k) * H * D];
+        if (VW == 4) {
+          const float4 v = *reinterpret_cast<const float4*>(u0 + (c + k) * cstride);
+          un[k][0] = v.x; un[k][1 % VW] = v.y; un[k][2 % VW] = v.z; un[k][3 % VW] = v.w;
+        } else {
+          un[k][0] = u0[(c + k) * cstride];
+        }
+      }
+    }
+#pragma unroll
+    for (int k = 0; k < U; ++k) {
+      if (c + k < nchunks) {
+        float* u = u0 + (c + k) * cstride;
+        if (VW == 4) *reinterpret_cast<float4*>(u) = make_float4(S[0], S[1 % VW], S[2 % VW], S[3 % VW]);
+        else u[0] = S[0];
+#pragma unroll
+        for (int j = 0; j < VW; ++j) S[j] = fmaf(gn[k], S[j], un[k][j]);
+      }
+    }
   }
-  *Sg = S;
+#pragma unroll
+  for (int j = 0; j < VW; ++j) Sg[j] = S[j];
 }
 
 template <typename T>
@@ -422,7 +454,7 @@ PCS_API int pcs_gla_chunk_prep(const pcs_gla_chunk_params* p, void* stream) {
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   if (smem > 48 * 1024)
     PCS_DISPATCH(p->dtype, PCS_CHECK_CUDA(cudaFuncSetAttribute(pcs::gla_chunk_prep_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, 220 * 1024)));
-  PCS_DISPATCH(p->dtype, pcs::gla_chunk_prep_kernel<T><<<dim3(p->n_chunks, p->heads), 256, smem, st>>>(*p));
+  PCS_DISPATCH(p->dtype, pcs::gla_chunk_prep_kernel<T><<<dim3(p->n_chunks, p->heads), pcs::kPrepThreads, smem, st>>>(*p));
   PCS_CHECK_CUDA(cudaGetLastError());
   pcs::count_launch();
   return PCS_OK;
@@ -435,7 +467,10 @@ PCS_API int pcs_gla_chunk_scan(const pcs_gla_chunk_params* p, void* stream) {
   PCS_REQUIRE(p->heads > 0 && p->heads <= 65535 && p->n_seqs <= 65535 && p->dim > 0 && p->vdim > 0, "pcs_gla_chunk_scan: bad sizes");
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   const long long elems = static_cast<long long>(p->dim) * p->vdim;
-  pcs::gla_chunk_scan_kernel<<<dim3(static_cast<unsigned>((elems + 255) / 256), p->heads, p->n_seqs), 256, 0, st>>>(*p);
+  if (p->vdim % 4 == 0 && ((reinterpret_cast<uintptr_t>(p->u) | reinterpret_cast<uintptr_t>(p->s_pool)) & 15) == 0)
+    pcs::gla_chunk_scan_kernel<4><<<dim3(static_cast<unsigned>((elems / 4 + 255) / 256), p->heads, p->n_seqs), 256, 0, st>>>(*p);
+  else
+    pcs::gla_chunk_scan_kernel<1><<<dim3(static_cast<unsigned>((elems + 255) / 256), p->heads, p->n_seqs), 256, 0, st>>>(*p);
   PCS_CHECK_CUDA(cudaGetLastError());
   pcs::count_launch();
   return PCS_OK;
@@ -464,7 +499,7 @@ PCS_API int pcs_gla_decay(const void* a, int64_t a_stride, const void* a2, const
     PCS_DISPATCH(dtype, pcs::gla_decay_tile_kernel<T><<<grid, 256, tile_smem, st>>>(static_cast<const T*>(a), a_stride, static_cast<const T*>(a2), a2_b, ld,
                                                                                    n_tokens, n_channels, rank, 1.f / tau));
   } else
-  PCS_DISPATCH(dtype, pcs::gla_decay_kernel<T><<<n_tokens, 256, rank * sizeof(float), st>>>(static_cast<const T*>(a), a_stride, static_cast<const T*>(a2),
+  PCS_DISPATCH(dtype, pcs::gla_decay_kernel<T><<<dim3(n_tokens, (n_channels + 255) / 256 > 64 ? 64 : (n_channels + 255) / 256), 256, rank * sizeof(float), st>>>(static_cast<const T*>(a), a_stride, static_cast<const T*>(a2),
                                                                                            a2_b, ld, n_channels, rank, 1.f / tau));
   PCS_CHECK_CUDA(cudaGetLastError());
   pcs::count_launch();

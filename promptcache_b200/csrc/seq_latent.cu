@@ -74,7 +74,8 @@ __global__ void __launch_bounds__(256) latent_q_kernel(const pcs_latent_q_params
   const T* q = static_cast<const T*>(p.q) + t * H * (D + R);
   const int lead = p.q_lat ? C : D;   // numbers in front of the rotated part of an output head
   T* qo = static_cast<T*>(p.q_out) + t * H * (lead + R);
-  for (int e = threadIdx.x; e < H * half; e += blockDim.x) {
+  const int tid0 = blockIdx.y * blockDim.x + threadIdx.x, nthr = gridDim.y * blockDim.x;   // a token's work is spread over gridDim.y blocks
+  for (int e = tid0; e < H * half; e += nthr) {
     const int h = e / half, i = e - h * half;
     const T* s = q + h * (D + R) + D;
     const float u = ldf(s + i), v = ldf(s + half + i);
@@ -84,12 +85,12 @@ __global__ void __launch_bounds__(256) latent_q_kernel(const pcs_latent_q_params
   }
   if (p.q_lat) {
     const T* ql = static_cast<const T*>(p.q_lat) + t * p.lat_tok_stride;
-    for (int e = threadIdx.x; e < H * C; e += blockDim.x) {
+    for (int e = tid0; e < H * C; e += nthr) {
       const int h = e / C, c = e - h * C;
       qo[h * (C + R) + c] = ql[h * p.lat_head_stride + c];
     }
   } else if (p.q_out != p.q) {
-    for (int e = threadIdx.x; e < H * D; e += blockDim.x) {
+    for (int e = tid0; e < H * D; e += nthr) {
       const int h = e / D, c = e - h * D;
       qo[h * (D + R) + c] = q[h * (D + R) + c];
     }
@@ -131,7 +132,7 @@ template <typename T>
 __global__ void __launch_bounds__(256) head_gate_kernel(const T* __restrict__ o, long long o_tok_stride, long long o_head_stride, const T* __restrict__ g,
                                                         long long g_stride, T* __restrict__ out, int H, int V) {
   const long long t = blockIdx.x;
-  for (int e = threadIdx.x; e < H * V; e += blockDim.x) {
+  for (int e = blockIdx.y * blockDim.x + threadIdx.x; e < H * V; e += gridDim.y * blockDim.x) {
     const int h = e / V, c = e - h * V;
     stf(out + t * H * V + e, ldf(o + t * o_tok_stride + h * o_head_stride + c) * sigmoidf_(ldf(g + t * g_stride + h)));
   }
@@ -161,7 +162,12 @@ PCS_API int pcs_latent_q(const pcs_latent_q_params* p, void* stream) {
               "pcs_latent_q: bad sizes H=%d dim=%d rot_dim=%d", p->n_heads, p->dim, p->rot_dim);
   PCS_REQUIRE(p->q_lat == nullptr || (p->kv_rank > 0 && p->q_out != p->q), "pcs_latent_q: latent queries need kv_rank and an output of their own");
   cudaStream_t st = static_cast<cudaStream_t>(stream);
-  PCS_DISPATCH(p->dtype, pcs::latent_q_kernel<T><<<p->n_tokens, 256, 0, st>>>(*p));
+  // few tokens (decoding): a token's copies are spread over several blocks, two elements per thread
+  const int per_token = p->n_heads * ((p->q_lat ? p->kv_rank : (p->q_out != p->q ? p->dim : 0)) + p->rot_dim / 2);
+  int ny = p->n_tokens >= 256 ? 1 : (per_token + 511) / 512;
+  if (ny > 64) ny = 64;
+  if (ny < 1) ny = 1;
+  PCS_DISPATCH(p->dtype, pcs::latent_q_kernel<T><<<dim3(p->n_tokens, ny), 256, 0, st>>>(*p));
   PCS_CHECK_CUDA(cudaGetLastError());
   pcs::count_launch();
   return PCS_OK;
@@ -196,7 +202,9 @@ PCS_API int pcs_head_gate(const void* o, int64_t o_tok_stride, int64_t o_head_st
   if (n_tokens == 0) return PCS_OK;
   PCS_REQUIRE(o && g && out && n_heads > 0 && vdim > 0, "pcs_head_gate: bad arguments");
   cudaStream_t st = static_cast<cudaStream_t>(stream);
-  PCS_DISPATCH(dtype, pcs::head_gate_kernel<T><<<n_tokens, 256, 0, st>>>(static_cast<const T*>(o), o_tok_stride, o_head_stride, static_cast<const T*>(g),
+  int ny = n_tokens >= 256 ? 1 : (n_heads * vdim + 511) / 512;
+  if (ny > 64) ny = 64;
+  PCS_DISPATCH(dtype, pcs::head_gate_kernel<T><<<dim3(n_tokens, ny), 256, 0, st>>>(static_cast<const T*>(o), o_tok_stride, o_head_stride, static_cast<const T*>(g),
                                                                         g_stride, static_cast<T*>(out), n_heads, vdim));
   PCS_CHECK_CUDA(cudaGetLastError());
   pcs::count_launch();

@@ -103,7 +103,8 @@ __global__ void __launch_bounds__(256) gate_norm_add_vec_kernel(const pcs_gna_pa
   for (int u = 0; u < PPT; ++u) {
     const int i = (threadIdx.x + u * 256) * N;
     if (i < W) {
-      ld16(y + i, v[u]);
+      if (p.y_f32) ldx(reinterpret_cast<const float*>(p.y) + static_cast<long long>(r) * p.y_stride + i, v[u]);
+      else ld16(y + i, v[u]);
       ld16(w + i, wv[u]);
       ldx(x + i, xv[u]);
       if (ls) ld16(ls + i, lv[u]);
@@ -291,7 +292,7 @@ PCS_API int pcs_gate_norm_add(const pcs_gna_params* p, void* stream) {
   const int piece = p->dtype == PCS_BF16 ? 8 : 4;
   const long long esz = p->dtype == PCS_BF16 ? 2 : 4;
   auto al = [](const void* q) { return (reinterpret_cast<uintptr_t>(q) & 15) == 0; };
-  const bool vec = !p->y_f32 && p->width % piece == 0 && p->width <= 512 * piece && (p->y_stride * esz) % 16 == 0 && al(p->x) && al(p->y) && al(p->w) &&
+  const bool vec = p->width % piece == 0 && p->width <= 512 * piece && (p->y_stride * (p->y_f32 ? 4 : esz)) % 16 == 0 && al(p->x) && al(p->y) && al(p->w) &&
                    (p->g == nullptr || (al(p->g) && (p->g_stride * esz) % 16 == 0)) && (p->ls == nullptr || al(p->ls)) &&
                    (p->next_w == nullptr || (al(p->next_w) && al(p->h_out)));
   if (vec) {
