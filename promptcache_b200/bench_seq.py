@@ -486,7 +486,21 @@ def safilorn_kernels(s: dict, dev, timer: Timer, prompt: int, ctx: int, hbm_gbs:
     wsd = nsq.attn_workspace(1, H, C, dev)
     ms = timer(lambda: nsq.attention(q1, pool, pool, o1, H, 0.1, None, None, True, b1, max_keys=cap, workspace=wsd, sink_logit=sink, v_row_stride=C + R), steps=15)
     out["attn_decode_latent"] = dict(gb(2.0 * (ctx + 1) * (C + R), ms), flops_per_byte=round(2.0 * H * (2 * C + R) / (2.0 * (C + R)), 1))
+    # the same at four times the context, where the kernels rather than the launches decide: the tensor-core kernel that stages a
+    # row once for 16 heads, and the plain kernel (one block per head and split) on the same rows
+    ctx4 = 4 * ctx
+    cap4 = ((ctx4 + 1 + 127) // 128) * 128
+    pool4, b4 = torch.randn(1, 1, cap4, C + R, device=dev).to(bf), nsq.Batch([0], [ctx4], [1], dev)
+    for impl, name in ((0, "attn_decode_latent_ctx%d" % ctx4), (2, "attn_decode_latent_plain_kernel_ctx%d" % ctx4)):
+        ms = timer(lambda: nsq.attention(q1, pool4, pool4, o1, H, 0.1, None, None, True, b4, impl=impl, max_keys=cap4, workspace=wsd, sink_logit=sink,
+                                         v_row_stride=C + R), steps=15)
+        out[name] = gb(2.0 * (ctx4 + 1) * (C + R), ms)
+    kp4, vp4 = torch.randn(1, G, cap4, D + R, device=dev).to(bf), torch.randn(1, G, cap4, V, device=dev).to(bf)
     qm, om = torch.randn(1, H * (D + R), device=dev).to(bf), torch.empty(1, H * V, device=dev, dtype=bf)
+    wsm = nsq.attn_workspace(1, H, V, dev)
+    ms = timer(lambda: nsq.attention(qm, kp4, vp4, om, H, 0.1, r1, r2, True, b4, max_keys=cap4, workspace=wsm), steps=15)
+    out["like_attn_decode_ctx%d" % ctx4] = gb(2.0 * G * (ctx4 + 1) * (D + R + V), ms)
+    del pool4, kp4, vp4
     wsm = nsq.attn_workspace(1, H, V, dev)
     ms = timer(lambda: nsq.attention(qm, kp, vp, om, H, 0.1, r1, r2, True, b1, max_keys=cap, workspace=wsm), steps=15)
     out["like_attn_decode"] = gb(2.0 * G * (ctx + 1) * (D + R + V), ms)

@@ -433,10 +433,15 @@ __global__ void __launch_bounds__(kAttnThreads) attn_combine_kernel(const pcs_at
   __syncthreads();
   const float inv = inv_s;
   T* o = static_cast<T*>(p.out) + (static_cast<long long>(t) * p.n_heads + h) * V;
-  for (int c = threadIdx.x; c < V; c += blockDim.x) {
+  // a block takes every gridDim.z-th group of 128 columns; a column's S values are requested together, then summed in order
+  for (int c = blockIdx.z * blockDim.x + threadIdx.x; c < V; c += gridDim.z * blockDim.x) {
+    float v[kAttnMaxSplits];
+#pragma unroll
+    for (int s = 0; s < kAttnMaxSplits; ++s) v[s] = s < S ? part[s * (V + 2) + 2 + c] : 0.f;
     float a = 0.f;
-#pragma unroll 4
-    for (int s = 0; s < S; ++s) a = fmaf(part[s * (V + 2) + 2 + c], fs[s], a);
+#pragma unroll
+    for (int s = 0; s < kAttnMaxSplits; ++s)
+      if (s < S) a = fmaf(v[s], fs[s], a);
     stf(o + c, a * inv);
   }
 }
@@ -472,6 +477,7 @@ PCS_API int pcs_qk_prep(const pcs_qkprep_params* p, void* stream) {
 
 namespace pcs {
 int launch_attn_tc(const pcs_attn_params& p, cudaStream_t st, bool* handled);
+int launch_attn_latent(const pcs_attn_params& p, cudaStream_t st, int* splits_out);
 }
 
 PCS_API int pcs_attn(const pcs_attn_params* p, void* stream) {
@@ -486,16 +492,26 @@ PCS_API int pcs_attn(const pcs_attn_params* p, void* stream) {
   PCS_REQUIRE((p->bias_r1 == nullptr) == (p->bias_r2 == nullptr), "pcs_attn: the distance bias needs both r1 and r2");
   PCS_REQUIRE(p->v_row_stride == 0 || p->v_row_stride >= p->vdim, "pcs_attn: the value row stride %d is below vdim %d", p->v_row_stride, p->vdim);
   cudaStream_t st = static_cast<cudaStream_t>(stream);
-  if (p->impl == 0) {
+  if (p->impl == 0) {  // (impl 2: the plain kernels with the split of the keys, never a tensor-core kernel)
     bool handled = false;
     if (int rc = pcs::launch_attn_tc(*p, st, &handled)) return rc;
     if (handled) return PCS_OK;
+    int latent_splits = 0;   // few tokens over rows that all heads share: the tensor-core kernel, then the merge of its partial results
+    if (p->max_len <= 4 && p->n_tokens <= 64) {
+      if (int rc = pcs::launch_attn_latent(*p, st, &latent_splits)) return rc;
+    }
+    if (latent_splits > 0) {
+      PCS_DISPATCH(p->dtype, pcs::attn_combine_kernel<T><<<dim3(p->n_tokens, p->n_heads, (p->vdim + pcs::kAttnThreads - 1) / pcs::kAttnThreads), pcs::kAttnThreads, 0, st>>>(*p, latent_splits));
+      PCS_CHECK_CUDA(cudaGetLastError());
+      pcs::count_launch();
+      return PCS_OK;
+    }
   }
   const size_t smem = static_cast<size_t>(p->dim + pcs::kAttnThreads) * sizeof(float);
   PCS_REQUIRE(smem <= 48 * 1024, "pcs_attn: dim %d exceeds the shared-memory query row", p->dim);
   // few tokens over many keys (decoding): the keys are split so that the launch fills the GPU; each split has >= 128 keys
   const int piece = p->dtype == PCS_BF16 ? 8 : 4;
-  const bool decode = p->impl == 0 && p->workspace != nullptr && p->dim % piece == 0 && p->vdim % piece == 0 &&
+  const bool decode = (p->impl == 0 || p->impl == 2) && p->workspace != nullptr && p->dim % piece == 0 && p->vdim % piece == 0 &&
                       p->vdim / piece <= pcs::kAttnThreads && p->v_row_stride % piece == 0;
   int splits = 1;
   if (p->workspace != nullptr && p->max_keys > 512) {
@@ -518,7 +534,7 @@ PCS_API int pcs_attn(const pcs_attn_params* p, void* stream) {
   PCS_CHECK_CUDA(cudaGetLastError());
   pcs::count_launch();
   if (splits > 1) {
-    PCS_DISPATCH(p->dtype, pcs::attn_combine_kernel<T><<<dim3(p->n_tokens, p->n_heads), pcs::kAttnThreads, 0, st>>>(*p, splits));
+    PCS_DISPATCH(p->dtype, pcs::attn_combine_kernel<T><<<dim3(p->n_tokens, p->n_heads, (p->vdim + pcs::kAttnThreads - 1) / pcs::kAttnThreads), pcs::kAttnThreads, 0, st>>>(*p, splits));
     PCS_CHECK_CUDA(cudaGetLastError());
     pcs::count_launch();
   }

@@ -226,7 +226,7 @@ class SafilornForCausalLM(SlotPoolCausalLM):
             q_lat = torch.bmm(q.view(T, H, D + R)[:, :, :D].transpose(0, 1), blk["uk_h"]).transpose(0, 1)   # [T, H, C]
             ql = nsq.latent_q(q, H, D, R, blk["freqs"], blk["rot_mult"], batch, q_lat=q_lat)
             o_lat = torch.empty(T, H * C, dtype=dt, device=dev)
-            ws = nsq.attn_workspace(T, H, C, dev) if T <= 16 else None
+            ws = nsq.attn_workspace(T, H, C, dev) if T <= 32 else None
             nsq.attention(ql, pool["ckv"], pool["ckv"], o_lat, H, blk["scale"], None, None, True, batch, impl=self.attn_impl, max_keys=self.pool.cap,
                           workspace=ws, sink_logit=blk["sink"], v_row_stride=C + R)
             o3 = torch.bmm(o_lat.view(T, H, C).transpose(0, 1), blk["uv_t"]).transpose(0, 1)                  # [T, H, V]

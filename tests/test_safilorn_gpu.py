@@ -171,12 +171,12 @@ def sink_attention(q, k, v, scale, sink, pos0=0):
 
 
 @pytest.mark.parametrize("dtype,H,D,V,N,T", [(F32, 3, 12, 8, 70, 70), (F32, 2, 10, 7, 45, 3), (BF16, 4, 48, 32, 300, 300), (BF16, 2, 24, 40, 700, 1), (F32, 2, 16, 8, 700, 1),
-                                              (BF16, 3, 64, 64, 200, 40)])
+                                              (BF16, 3, 64, 64, 200, 40), (BF16, 16, 72, 8, 700, 1), (BF16, 20, 40, 8, 130, 3), (BF16, 5, 264, 8, 90, 2)])
 def test_attention_with_a_learned_sink_per_head(nsq, dtype, H, D, V, N, T):
     """Multi-head rows (the expanded form) and one shared row per key whose leading numbers are the values (the latent form)."""
     g = torch.Generator().manual_seed(N + T)
     rnd = lambda *s: torch.randn(*s, generator=g, dtype=F64).to(dtype).to(F64)
-    sink = torch.tensor([2.5, -1.0, 0.3, 6.0][:H], dtype=F64)
+    sink = torch.tensor(([2.5, -1.0, 0.3, 6.0] * 5)[:H], dtype=F64)
     pos0, tol = N - T, (3e-6 if dtype == F32 else 1.2e-2)
     b = batch_of(nsq, [1], [pos0], [T])
     q, k, v = rnd(T, H, D) * 0.7, rnd(N, H, D), rnd(N, H, V)
