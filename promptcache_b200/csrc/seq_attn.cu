@@ -404,7 +404,7 @@ __global__ void __launch_bounds__(kAttnThreads) attn_decode_kernel(const pcs_att
   }
 }
 
-constexpr int kAttnMaxSplits = 32;
+constexpr int kAttnMaxSplits = 64;
 
 // Merge of the splits' partial results.  The splits' maxima and sums are read by one thread each, the common maximum, the total
 // and every split's factor exp(m_s - M) are formed once in shared memory, and the columns then need independent loads only.

@@ -17,6 +17,7 @@ namespace pcs {
 namespace {
 
 constexpr int LB_N = 64, LB_THREADS = 128, LB_PAD = 8, LB_HEADS = 16;
+constexpr int kLatentMaxSplits = 64;  // what the merge kernel and the workspace size of pcs_attn_workspace_floats allow
 
 template <int NT>  // n8 tiles of value columns per warp: the kernel serves vdim <= 4 * NT * 8
 __global__ void __launch_bounds__(LB_THREADS) attn_latent_kernel(const pcs_attn_params p, int DKP) {
@@ -208,7 +209,7 @@ int launch_attn_latent(const pcs_attn_params& p, cudaStream_t st, int* splits_ou
   const long long blocks = static_cast<long long>(p.n_tokens) * groups;
   const int want = static_cast<int>((2 * 148 + blocks - 1) / blocks);
   if (splits > want) splits = want;
-  if (splits > 32) splits = 32;
+  if (splits > kLatentMaxSplits) splits = kLatentMaxSplits;
   if (splits < 1) splits = 1;
   if (p.workspace_floats < static_cast<long long>(p.n_tokens) * p.n_heads * splits * (p.vdim + 2)) return PCS_OK;
   *splits_out = splits;

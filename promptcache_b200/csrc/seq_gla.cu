@@ -371,8 +371,8 @@ __global__ void __launch_bounds__(kPrepThreads) gla_chunk_prep_kernel(const pcs_
   }
 }
 
-// One thread per VW neighbouring value columns of one state row: the entry's chunks in order.  The sums and decays of four
-// chunks are requested before the dependent chain S <- g S + u runs over them, so four loads per thread are in flight.
+// One thread per VW neighbouring value columns of one state row: the entry's chunks in order.  The sums and decays of eight
+// chunks are requested before the dependent chain S <- g S + u runs over them, so eight loads per thread are in flight.
 template <int VW>
 __global__ void __launch_bounds__(256) gla_chunk_scan_kernel(const pcs_gla_chunk_params p) {
   const int D = p.dim, V = p.vdim, H = p.heads;
@@ -390,7 +390,7 @@ __global__ void __launch_bounds__(256) gla_chunk_scan_kernel(const pcs_gla_chunk
   const long long cstride = static_cast<long long>(H) * D * V;
   float* u0 = p.u + (static_cast<long long>(c0) * H + head) * D * V + e;
   const float* g0 = p.g + (static_cast<long long>(c0) * H + head) * D + d;
-  constexpr int U = 4;
+  constexpr int U = 8;
   for (int c = 0; c < nchunks; c += U) {
     float un[U][VW], gn[U];
 #pragma unroll
