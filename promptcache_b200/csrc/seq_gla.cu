@@ -268,26 +268,44 @@ __global__ void __launch_bounds__(512) gla_scan_reg_kernel(const pcs_gla_params 
   }
 }
 
-// out[t, head, :] = o / rms(o) * norm_w * silu(g): one warp per (token, head), eight per block.
+// out[t, head, :] = o / rms(o) * norm_w * silu(g): one block of kOutThreads per (token, head); a thread's columns, their gates and
+// norm weights are requested together before the reduction.
+constexpr int kOutThreads = 128, kOutCols = 4;   // up to kOutThreads * kOutCols columns stay in registers
 template <typename T>
-__global__ void __launch_bounds__(256) gla_out_kernel(const pcs_gla_params p) {
-  const int V = p.vdim, H = p.heads, lane = threadIdx.x & 31;
-  const long long item = static_cast<long long>(blockIdx.x) * 8 + (threadIdx.x >> 5);
-  if (item >= static_cast<long long>(p.n_tokens) * H) return;
-  const long long t = item / H;
-  const int head = static_cast<int>(item - t * H);
-  const float* o = p.o_raw + t * (static_cast<long long>(H) * V) + head * V;
-  const T* g = static_cast<const T*>(p.proj) + t * p.row_stride + p.g_off + head * V;
-  const T* nw = static_cast<const T*>(p.norm_w);
+__device__ __forceinline__ void gla_head_out(const float* __restrict__ o, const T* __restrict__ g, const T* __restrict__ nw, T* __restrict__ out, int V,
+                                             float eps, float* red) {
+  float ov[kOutCols], gv[kOutCols], wv[kOutCols];
   float ss = 0.f;
-  for (int c = lane; c < V; c += 32) ss = fmaf(o[c], o[c], ss);
-  ss = warp_sum(ss);
-  const float inv = 1.f / sqrtf(ss / static_cast<float>(V) + p.eps);
-  T* out = static_cast<T*>(p.out) + t * (static_cast<long long>(H) * V) + head * V;
-  for (int c = lane; c < V; c += 32) {
-    const float gv = ldf(g + c);
-    stf(out + c, o[c] * inv * ldf(nw + c) * (gv * sigmoidf_(gv)));
+#pragma unroll
+  for (int u = 0; u < kOutCols; ++u) {
+    const int c = threadIdx.x + u * kOutThreads;
+    ov[u] = c < V ? o[c] : 0.f;
+    gv[u] = c < V ? ldf(g + c) : 0.f;
+    wv[u] = c < V ? ldf(nw + c) : 0.f;
   }
+#pragma unroll
+  for (int u = 0; u < kOutCols; ++u) ss = fmaf(ov[u], ov[u], ss);
+  for (int c = threadIdx.x + kOutCols * kOutThreads; c < V; c += kOutThreads) ss = fmaf(o[c], o[c], ss);
+  ss = block_sum(ss, red);
+  const float inv = 1.f / sqrtf(ss / static_cast<float>(V) + eps);
+#pragma unroll
+  for (int u = 0; u < kOutCols; ++u) {
+    const int c = threadIdx.x + u * kOutThreads;
+    if (c < V) stf(out + c, ov[u] * inv * wv[u] * (gv[u] * sigmoidf_(gv[u])));
+  }
+  for (int c = threadIdx.x + kOutCols * kOutThreads; c < V; c += kOutThreads) {
+    const float x = ldf(g + c);
+    stf(out + c, o[c] * inv * ldf(nw + c) * (x * sigmoidf_(x)));
+  }
+}
+
+template <typename T>
+__global__ void __launch_bounds__(kOutThreads) gla_out_kernel(const pcs_gla_params p) {
+  __shared__ float red[33];
+  const int V = p.vdim, H = p.heads, head = blockIdx.y;
+  const long long t = blockIdx.x;
+  gla_head_out<T>(p.o_raw + t * (static_cast<long long>(H) * V) + head * V, static_cast<const T*>(p.proj) + t * p.row_stride + p.g_off + head * V,
+                  static_cast<const T*>(p.norm_w), static_cast<T*>(p.out) + t * (static_cast<long long>(H) * V) + head * V, V, p.eps, red);
 }
 
 // ---- the chunkwise form (prompts) -------------------------------------------------------------------------------------
@@ -349,6 +367,16 @@ __global__ void __launch_bounds__(kPrepThreads) gla_chunk_prep_kernel(const pcs_
   // B_i broadcast).  Pairs above the diagonal, and rows past the chunk's end, are zero.
   float* a = p.a + base * C * C;
   for (int e = tid; e < C * C; e += kPrepThreads) a[e] = 0.f;
+  // bfloat16 projections: the pair factors go through the base-2 exponential unit (relative error 2^-22, far below the operands'
+  // rounding), with the running sums rescaled once; float32 runs keep the library exponential
+  constexpr bool kFast = sizeof(T) == 2;
+  __syncthreads();
+  if (kFast) {
+    for (int e = tid; e < C * D; e += kPrepThreads) {
+      const int i = e / D, d = e - i * D;
+      Bs[i * DP + d] *= 1.4426950408889634f;
+    }
+  }
   __syncthreads();
   const int half = (C + 1) / 2;
   for (int e = tid; e < half * (C + 1); e += kPrepThreads) {
@@ -363,10 +391,10 @@ __global__ void __launch_bounds__(kPrepThreads) gla_chunk_prep_kernel(const pcs_
     float a0 = 0.f, a1 = 0.f;
     int d = 0;
     for (; d + 1 < D; d += 2) {
-      a0 = fmaf(qi[d] * kk[d], expf(bi[d] - bs[d]), a0);
-      a1 = fmaf(qi[d + 1] * kk[d + 1], expf(bi[d + 1] - bs[d + 1]), a1);
+      a0 = fmaf(qi[d] * kk[d], kFast ? ex2(bi[d] - bs[d]) : expf(bi[d] - bs[d]), a0);
+      a1 = fmaf(qi[d + 1] * kk[d + 1], kFast ? ex2(bi[d + 1] - bs[d + 1]) : expf(bi[d + 1] - bs[d + 1]), a1);
     }
-    if (d < D) a0 = fmaf(qi[d] * kk[d], expf(bi[d] - bs[d]), a0);
+    if (d < D) a0 = fmaf(qi[d] * kk[d], kFast ? ex2(bi[d] - bs[d]) : expf(bi[d] - bs[d]), a0);
     a[i * C + s_] = a0 + a1;
   }
 }
@@ -421,25 +449,13 @@ __global__ void __launch_bounds__(256) gla_chunk_scan_kernel(const pcs_gla_chunk
 }
 
 template <typename T>
-__global__ void __launch_bounds__(256) gla_chunk_out_kernel(const pcs_gla_chunk_params p) {
-  const int V = p.vdim, H = p.heads, C = p.chunk, lane = threadIdx.x & 31;
-  const long long item = static_cast<long long>(blockIdx.x) * 8 + (threadIdx.x >> 5);
-  if (item >= static_cast<long long>(p.n_tokens) * H) return;
-  const long long t = item / H;
-  const int head = static_cast<int>(item - t * H);
+__global__ void __launch_bounds__(kOutThreads) gla_chunk_out_kernel(const pcs_gla_chunk_params p) {
+  __shared__ float red[33];
+  const int V = p.vdim, H = p.heads, C = p.chunk, head = blockIdx.y;
+  const long long t = blockIdx.x;
   const int row = p.tok_row[t];
-  const float* o = p.o + ((static_cast<long long>(row / C) * H + head) * C + row % C) * V;
-  const T* g = static_cast<const T*>(p.proj) + t * p.row_stride + p.g_off + head * V;
-  const T* nw = static_cast<const T*>(p.norm_w);
-  float ss = 0.f;
-  for (int c = lane; c < V; c += 32) ss = fmaf(o[c], o[c], ss);
-  ss = warp_sum(ss);
-  const float inv = 1.f / sqrtf(ss / static_cast<float>(V) + p.eps);
-  T* out = static_cast<T*>(p.out) + t * (static_cast<long long>(H) * V) + head * V;
-  for (int c = lane; c < V; c += 32) {
-    const float gv = ldf(g + c);
-    stf(out + c, o[c] * inv * ldf(nw + c) * (gv * sigmoidf_(gv)));
-  }
+  gla_head_out<T>(p.o + ((static_cast<long long>(row / C) * H + head) * C + row % C) * V, static_cast<const T*>(p.proj) + t * p.row_stride + p.g_off + head * V,
+                  static_cast<const T*>(p.norm_w), static_cast<T*>(p.out) + t * (static_cast<long long>(H) * V) + head * V, V, p.eps, red);
 }
 
 }  // namespace pcs
@@ -481,8 +497,7 @@ PCS_API int pcs_gla_chunk_out(const pcs_gla_chunk_params* p, void* stream) {
   if (p->n_tokens == 0) return PCS_OK;
   PCS_REQUIRE(p->proj && p->o && p->tok_row && p->norm_w && p->out && p->chunk > 0 && p->heads > 0 && p->vdim > 0, "pcs_gla_chunk_out: bad arguments");
   cudaStream_t st = static_cast<cudaStream_t>(stream);
-  const long long items = static_cast<long long>(p->n_tokens) * p->heads;
-  PCS_DISPATCH(p->dtype, pcs::gla_chunk_out_kernel<T><<<static_cast<unsigned>((items + 7) / 8), 256, 0, st>>>(*p));
+  PCS_DISPATCH(p->dtype, pcs::gla_chunk_out_kernel<T><<<dim3(p->n_tokens, p->heads), pcs::kOutThreads, 0, st>>>(*p));
   PCS_CHECK_CUDA(cudaGetLastError());
   pcs::count_launch();
   return PCS_OK;
@@ -558,8 +573,7 @@ PCS_API int pcs_gla_scan(const pcs_gla_params* p, void* stream) {
     PCS_DISPATCH(p->dtype, pcs::gla_scan_kernel<T><<<grid, threads, smem, st>>>(*p, VS, R));
     PCS_CHECK_CUDA(cudaGetLastError());
   }
-  const long long items = static_cast<long long>(p->n_tokens) * p->heads;
-  PCS_DISPATCH(p->dtype, pcs::gla_out_kernel<T><<<static_cast<unsigned>((items + 7) / 8), 256, 0, st>>>(*p));
+  PCS_DISPATCH(p->dtype, pcs::gla_out_kernel<T><<<dim3(p->n_tokens, p->heads), pcs::kOutThreads, 0, st>>>(*p));
   PCS_CHECK_CUDA(cudaGetLastError());
   pcs::count_launch(2);
   return PCS_OK;
