@@ -316,6 +316,7 @@ def xielu(z: torch.Tensor, out: torch.Tensor, a: torch.Tensor) -> None:
 
 
 LINEAR_ROWS_MAX = 8
+ATTN_MAX_VDIM = 512   # value columns per head that every attention kernel serves
 
 
 def linear(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] = None, kernel: Optional[bool] = None) -> torch.Tensor:

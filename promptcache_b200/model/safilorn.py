@@ -140,7 +140,9 @@ class SafilornForCausalLM(SlotPoolCausalLM):
                            w_ukv=torch.cat([uk, uv], 0).contiguous(),             # latents -> plain key parts of all heads, then values
                            uk_h=uk.view(H, D, C).contiguous(),                    # per head: carries a query into the latent space
                            uv_t=uv.view(H, V, C).transpose(1, 2).contiguous(),    # per head [C, V]: carries a latent result back
-                           sink=f32(p + "mix.sink").reshape(-1), w_o=get(p + "mix.o"), spec=LatentKVSpec(C, R))
+                           sink=f32(p + "mix.sink").reshape(-1), w_o=get(p + "mix.o"), spec=LatentKVSpec(C, R),
+                           # the latent form's result per head is kv_rank wide: beyond what the decoding kernels hold, only the expanded form runs
+                           latent_ok=C <= nsq.ATTN_MAX_VDIM)
             else:
                 H, D, V = (int(m[k]) for k in ("heads", "dim", "vdim"))
                 a1 = get(p + "mix.a1")
@@ -176,6 +178,8 @@ class SafilornForCausalLM(SlotPoolCausalLM):
         self.latent_form = None      # None: by step (prompts expanded, decoding in the latent space); "expanded" / "latent" force one
         self.expand_min_len = 16     # steps whose longest entry brings at least this many tokens attend over expanded keys
         self._init_runtime(dev, max_tokens)
+        if not all(b.get("latent_ok", True) for b in self.blocks):
+            self.use_cuda_graphs = False   # the expanded form describes the step's context on the host: it is not recorded
 
     def state_specs(self):
         return [b["spec"] for b in self.blocks]
@@ -209,6 +213,8 @@ class SafilornForCausalLM(SlotPoolCausalLM):
         q = nsq.linear(cq, blk["w_uq"])                      # [T, H * (D + R)], per head [plain | rotated]
         # a recorded decoding step reads everything that changes from device buffers: only the latent form does
         form = "latent" if torch.cuda.is_current_stream_capturing() else (self.latent_form or ("expanded" if batch.max_len >= self.expand_min_len else "latent"))
+        if not blk["latent_ok"]:
+            form = "expanded"
         if form == "expanded":
             ctx, ids = self._context(batch, step)
             c_ctx = nsq.latent_gather(pool["ckv"], C, ctx)

@@ -359,10 +359,12 @@ def layer_sets():
                 A(heads=5, dim=6, rot_dim=2, vdim=3, kv_rank=4, q_rank=7, mlp=None), G(heads=3, dim=5, vdim=3, mlp="moe", experts=1, top=1, ff=7)],
         "attention_only": [A(mlp="moe"), A(heads=4, dim=8, rot_dim=8, vdim=16, kv_rank=8, q_rank=8, base=50.0)],
         "recurrent_only": [G(mlp="dense"), G(heads=4, dim=16, vdim=8, low_rank=3)],
+        # a latent wider than the decoding kernels' value rows: the expanded form serves decoding too
+        "wide_latent": [A(heads=2, dim=8, rot_dim=4, vdim=8, kv_rank=520, q_rank=8), G(mlp=None)],
     }
 
 
-@pytest.mark.parametrize("name,width", [("mixed", 40), ("mixed", 24), ("odd", 30), ("odd", 37), ("attention_only", 64), ("recurrent_only", 48)])
+@pytest.mark.parametrize("name,width", [("mixed", 40), ("mixed", 24), ("odd", 30), ("odd", 37), ("attention_only", 64), ("recurrent_only", 48), ("wide_latent", 32)])
 def test_model_whole_prompt_against_oracle(tmp_path, name, width):
     cfg = O.make_config(layer_sets()[name], width=width, embed_scale=width ** 0.5)
     W = O.random_model(cfg, seed=width)
@@ -378,6 +380,9 @@ def test_model_whole_prompt_against_oracle(tmp_path, name, width):
             xs = [W["embed"].to(F64)[torch.tensor(toks)] * cfg["embedding"]["scale"]] + trace
             close(m.layer_trace[i], sum(a[j] * xs[j] for j in range(i + 2)), 3e-5, f"stream after layer {i} ({form})")
         close(got, want, 5e-5, f"logits, float32 ({form})")
+    seq = m.new_sequence()   # (the last float32 model) prompt, then token by token
+    got = torch.cat([m.step([(seq, toks[:20])], [list(range(20))])] + [m.step([(seq, [t])]) for t in toks[20:]])
+    close(got, want, 5e-5, "logits, float32, decoded")
     mb = load(tmp_path, cfg, W, BF16, "b")
     gb = mb.step([(mb.new_sequence(), toks)], [list(range(len(toks)))])
     # (heads of five or six numbers and three-way routers make bfloat16 rounding and flipped choices weigh more in the odd set)
