@@ -313,6 +313,7 @@ typedef struct pcs_combine_params {
   float mult;
   int32_t n_tokens, width, top, n_experts, dtype, y_dtype;
   const int32_t* y_row;     /* [n_tokens * top] or NULL */
+  int32_t overwrite;        /* 1: x = mult * (...) instead of x += (x need not be initialised) */
 } pcs_combine_params;
 int pcs_moe_combine(const pcs_combine_params* p, void* stream);
 
@@ -323,7 +324,9 @@ int pcs_glu_mul(const void* gu, int64_t gu_stride, void* out, int n_rows, int ff
 
 /* Depth-weighted average: out[r, :] = sum_{j < n_terms} coef[j] * xs[j][row(r), :], row(r) = rows ? rows[r] : r, where xs[j] is the
  * fp32 matrix at xs + j * term_stride elements.  x_out (fp32 [n_rows, width]) may be NULL; when next_w is given,
- * h_out[r, :] = rms(out[r, :]) * (w_offset + next_w)  (`dtype`).  The sum runs over j in increasing order. */
+ * h_out[r, :] = rms(out[r, :]) * (w_offset + next_w)  (`dtype`).  The sum runs over j in increasing order.
+ * With y (a sublayer's result, `dtype` or fp32, [*, y_stride]) the newest term first takes its residual sum,
+ * xs[n_terms - 1][row, :] += (w_offset + y_w) * rms(y[row, :]), as pcs_gate_norm_add would have done (every row at most once). */
 typedef struct pcs_depthmix_params {
   const float* xs;
   int64_t term_stride;
@@ -334,7 +337,11 @@ typedef struct pcs_depthmix_params {
   const void* next_w;       /* [width] `dtype` or NULL */
   void* h_out;              /* [n_rows, width] `dtype` */
   float w_offset, eps;
-  int32_t n_rows, width, dtype, reserved;
+  int32_t n_rows, width, dtype;
+  int32_t y_f32;            /* y is fp32 */
+  const void* y;            /* or NULL */
+  int64_t y_stride;
+  const void* y_w;          /* [width] `dtype` */
 } pcs_depthmix_params;
 int pcs_depth_mix(const pcs_depthmix_params* p, void* stream);
 

@@ -82,7 +82,8 @@ class pcs_glu_act(C.Structure):
 class pcs_depthmix_params(C.Structure):
     _fields_ = [("xs", C.c_void_p), ("term_stride", C.c_int64), ("n_terms", C.c_int32), ("coef", C.c_void_p), ("rows", C.c_void_p),
                 ("x_out", C.c_void_p), ("next_w", C.c_void_p), ("h_out", C.c_void_p), ("w_offset", C.c_float), ("eps", C.c_float),
-                ("n_rows", C.c_int32), ("width", C.c_int32), ("dtype", C.c_int32), ("reserved", C.c_int32)]
+                ("n_rows", C.c_int32), ("width", C.c_int32), ("dtype", C.c_int32), ("y_f32", C.c_int32), ("y", C.c_void_p), ("y_stride", C.c_int64),
+                ("y_w", C.c_void_p)]
 
 
 class pcs_latent_prep_params(C.Structure):
@@ -126,7 +127,7 @@ class pcs_combine_params(C.Structure):
     _fields_ = [("x", C.c_void_p), ("y", C.c_void_p), ("idx", C.c_void_p), ("wgt", C.c_void_p), ("h", C.c_void_p), ("h_stride", C.c_int64),
                 ("ys", C.c_void_p), ("ys_stride", C.c_int64), ("shared_gate", C.c_void_p), ("mult", C.c_float),
                 ("n_tokens", C.c_int32), ("width", C.c_int32), ("top", C.c_int32), ("n_experts", C.c_int32), ("dtype", C.c_int32),
-                ("y_dtype", C.c_int32), ("y_row", C.c_void_p)]
+                ("y_dtype", C.c_int32), ("y_row", C.c_void_p), ("overwrite", C.c_int32)]
 
 
 class pcs_mlstm_params(C.Structure):
@@ -623,9 +624,11 @@ def moe_experts(h: torch.Tensor, idx: torch.Tensor, w_gu: torch.Tensor, w_down: 
 
 
 def moe_combine(x: torch.Tensor, y: Optional[torch.Tensor], idx: torch.Tensor, wgt: torch.Tensor, h: torch.Tensor, n_experts: int, mult: float,
-                ys: Optional[torch.Tensor] = None, shared_gate: Optional[torch.Tensor] = None, y_row: Optional[torch.Tensor] = None) -> None:
+                ys: Optional[torch.Tensor] = None, shared_gate: Optional[torch.Tensor] = None, y_row: Optional[torch.Tensor] = None,
+                overwrite: bool = False) -> None:
     """x += mult * (sum_k wgt[:, k] * (y of the choice, or h itself for a choice >= n_experts) + shared_gate * ys).  y is float32 or
-    in h's type; `y_row` maps pair t * top + k to its row of y (None: the pair's own index)."""
+    in h's type; `y_row` maps pair t * top + k to its row of y (None: the pair's own index).  `overwrite`: x = mult * (...) instead
+    (x may be uninitialised)."""
     _cuda(x, y, idx, wgt, h, ys, shared_gate, y_row)
     dt = h.dtype
     _rows2d(h, dt, "moe_combine: h")
@@ -646,6 +649,7 @@ def moe_combine(x: torch.Tensor, y: Optional[torch.Tensor], idx: torch.Tensor, w
     p.ys, p.ys_stride, p.shared_gate, p.mult = _ptr(ys), ys.stride(0) if ys is not None else 0, _ptr(shared_gate), float(mult)
     p.n_tokens, p.width, p.top, p.n_experts, p.dtype = T, x.shape[1], top, int(n_experts), dtype_code(dt)
     p.y_dtype, p.y_row = (PCS_F32 if (y is None or y.dtype == torch.float32) else dtype_code(dt)), _ptr(y_row)
+    p.overwrite = 1 if overwrite else 0
     _check(load().pcs_moe_combine(C.byref(p), _stream()), "pcs_moe_combine")
 
 
@@ -668,10 +672,16 @@ def glu_mul(gu: torch.Tensor, ff: int, act=None) -> torch.Tensor:
 
 
 def depth_mix(xs: torch.Tensor, n_terms: int, coef: torch.Tensor, eps: float, x_out: Optional[torch.Tensor] = None, next_w: Optional[torch.Tensor] = None,
-              h_out: Optional[torch.Tensor] = None, w_offset: float = 0.0, rows: Optional[torch.Tensor] = None) -> None:
+              h_out: Optional[torch.Tensor] = None, w_offset: float = 0.0, rows: Optional[torch.Tensor] = None, y: Optional[torch.Tensor] = None,
+              y_w: Optional[torch.Tensor] = None) -> None:
     """out = sum_{j < n_terms} coef[j] * xs[j] over float32 xs [terms, T, width] (at the rows `rows` when given); x_out gets the sum,
-    h_out = rms_norm(out) * (w_offset + next_w)."""
-    _cuda(xs, coef, x_out, next_w, h_out, rows)
+    h_out = rms_norm(out) * (w_offset + next_w).  With y [T, width] (y_w's type or float32) and y_w, xs[n_terms - 1] first takes the
+    residual sum xs[n_terms - 1] += (w_offset + y_w) * rms_norm(y) in place (without `rows`: every row once)."""
+    _cuda(xs, coef, x_out, next_w, h_out, rows, y, y_w)
+    if y is not None:
+        if y_w is None or rows is not None or y.dim() != 2 or y.stride(1) != 1 or tuple(y.shape) != tuple(xs.shape[1:]) or y.dtype not in (torch.float32, y_w.dtype) \
+                or not y_w.is_contiguous() or y_w.numel() != xs.shape[2] or (next_w is not None and next_w.dtype != y_w.dtype):
+            raise NativeError("depth_mix: y must be [T, width] in y_w's type or float32, y_w [width], and no row subset")
     if xs.dtype != torch.float32 or xs.dim() != 3 or not xs.is_contiguous() or not 0 < n_terms <= xs.shape[0]:
         raise NativeError("depth_mix: xs must be contiguous float32 [terms, T, width]")
     if coef.dtype != torch.float32 or not coef.is_contiguous() or coef.numel() < n_terms:
@@ -687,7 +697,10 @@ def depth_mix(xs: torch.Tensor, n_terms: int, coef: torch.Tensor, eps: float, x_
     p = pcs_depthmix_params()
     p.xs, p.term_stride, p.n_terms, p.coef, p.rows = xs.data_ptr(), xs.stride(0), int(n_terms), coef.data_ptr(), _ptr(rows)
     p.x_out, p.next_w, p.h_out, p.w_offset, p.eps = _ptr(x_out), _ptr(next_w), _ptr(h_out), float(w_offset), float(eps)
-    p.n_rows, p.width, p.dtype = R, xs.shape[2], dtype_code(next_w.dtype if next_w is not None else torch.float32)
+    wt = next_w if next_w is not None else y_w
+    p.n_rows, p.width, p.dtype = R, xs.shape[2], dtype_code(wt.dtype if wt is not None else torch.float32)
+    if y is not None:
+        p.y, p.y_stride, p.y_w, p.y_f32 = y.data_ptr(), y.stride(0), y_w.data_ptr(), 1 if (y.dtype == torch.float32 and y_w.dtype != torch.float32) else 0
     _check(load().pcs_depth_mix(C.byref(p), _stream()), "pcs_depth_mix")
 
 

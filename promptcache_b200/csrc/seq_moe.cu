@@ -262,9 +262,14 @@ __global__ void __launch_bounds__(256) moe_combine_kernel(const pcs_combine_para
 #pragma unroll
         for (int e = 0; e < N; ++e) a[e] = fmaf(sg, v[e], a[e]);
       }
-      ldx(x + i, xv);
+      if (p.overwrite) {
 #pragma unroll
-      for (int e = 0; e < N; ++e) xv[e] = fmaf(p.mult, a[e], xv[e]);
+        for (int e = 0; e < N; ++e) xv[e] = p.mult * a[e];
+      } else {
+        ldx(x + i, xv);
+#pragma unroll
+        for (int e = 0; e < N; ++e) xv[e] = fmaf(p.mult, a[e], xv[e]);
+      }
       stx(x + i, xv);
     }
   } else {
@@ -276,7 +281,7 @@ __global__ void __launch_bounds__(256) moe_combine_kernel(const pcs_combine_para
         a = fmaf(w_s[k], v, a);
       }
       if (ys) a = fmaf(sg, ldf(ys + i), a);
-      x[i] = fmaf(p.mult, a, x[i]);
+      x[i] = p.overwrite ? p.mult * a : fmaf(p.mult, a, x[i]);
     }
   }
 }

@@ -197,6 +197,22 @@ __global__ void __launch_bounds__(256) depth_mix_kernel(const pcs_depthmix_param
   const int r = blockIdx.x, W = p.width;
   const long long row = p.rows ? p.rows[r] : r;
   const float* src = p.xs + row * W;
+  if (p.y) {  // the newest term's residual sum first: x += (offset + w) * rms(y)
+    float* xl = const_cast<float*>(src) + static_cast<long long>(p.n_terms - 1) * p.term_stride;
+    const T* y = static_cast<const T*>(p.y) + row * p.y_stride;
+    const float* y32 = p.y_f32 ? static_cast<const float*>(p.y) + row * p.y_stride : nullptr;
+    const T* yw = static_cast<const T*>(p.y_w);
+    float sy = 0.f;
+    for (int i = threadIdx.x; i < W; i += blockDim.x) {
+      const float v = y32 ? y32[i] : ldf(y + i);
+      u[i] = v;
+      sy = fmaf(v, v, sy);
+    }
+    sy = block_sum(sy, red);
+    const float inv_y = 1.f / sqrtf(sy / static_cast<float>(W) + p.eps);
+    for (int i = threadIdx.x; i < W; i += blockDim.x) xl[i] += (p.w_offset + ldf(yw + i)) * u[i] * inv_y;
+    __syncthreads();  // the sum below reads the row with another thread mapping
+  }
   const bool vec = (W & 3) == 0 && (p.term_stride & 3) == 0 && (reinterpret_cast<uintptr_t>(p.xs) & 15) == 0;
   float ss = 0.f;
   if (vec) {
@@ -239,6 +255,7 @@ PCS_API int pcs_depth_mix(const pcs_depthmix_params* p, void* stream) {
   PCS_REQUIRE(p->xs && p->coef && p->n_terms > 0 && p->n_rows > 0 && p->width > 0, "pcs_depth_mix: bad arguments");
   PCS_REQUIRE(p->x_out || p->next_w, "pcs_depth_mix: nothing to write");
   PCS_REQUIRE(p->next_w == nullptr || p->h_out != nullptr, "pcs_depth_mix: next_w needs h_out");
+  PCS_REQUIRE(p->y == nullptr || p->y_w != nullptr, "pcs_depth_mix: the residual sum needs its norm weight");
   const size_t smem = static_cast<size_t>(p->width) * sizeof(float);
   PCS_REQUIRE(smem <= 200 * 1024, "pcs_depth_mix: width %d exceeds the shared-memory row", p->width);
   cudaStream_t st = static_cast<cudaStream_t>(stream);

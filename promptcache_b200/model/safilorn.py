@@ -256,8 +256,8 @@ class SafilornForCausalLM(SlotPoolCausalLM):
         if mode is None and torch.cuda.is_current_stream_capturing():
             mode = False if T * blk["top"] <= 256 else "own"   # a recorded decoding step keeps to this library's own kernels
         ye, rows_e = nsq.moe_experts(h, idx, blk["we_gu"], blk["we_down"], grouped=mode, act=blk["act"])
-        y = torch.zeros(T, W, dtype=torch.float32, device=dev)
-        nsq.moe_combine(y, ye, idx, wgt, h, blk["n_experts"], 1.0, y_row=rows_e)
+        y = torch.empty(T, W, dtype=torch.float32, device=dev)
+        nsq.moe_combine(y, ye, idx, wgt, h, blk["n_experts"], 1.0, y_row=rows_e, overwrite=True)
         return y
 
     # ---- the layers over one batch ------------------------------------------------------------------------------
@@ -275,15 +275,22 @@ class SafilornForCausalLM(SlotPoolCausalLM):
             x, pool = xs[i + 1], self.pool.layers[i]
             y = self._latent_attention(h, blk, pool, batch, step) if blk["type"] == "latent_attention" else self._gla(h, blk, pool, batch)
             kind = blk["mlp"]
-            nsq.gate_norm_add(x, y, None, blk["norm1b"], None, eps, blk["norm2"] if kind else None, h if kind else None, w_offset=off)
-            if kind == "dense":
-                gu = nsq.linear(h, blk["w_gu"], blk["b_gu"])
-                d = nsq.linear(nsq.glu_mul(gu, blk["ff"]), blk["w_down"], blk["b_down"])
-                nsq.gate_norm_add(x, d, None, blk["norm2b"], None, eps, w_offset=off)
-            elif kind == "moe":
-                nsq.gate_norm_add(x, self._moe(h, blk), None, blk["norm2b"], None, eps, w_offset=off)
-            if i + 1 < L:
-                nsq.depth_mix(xs, i + 2, blk["depth"], eps, x_out=xs[i + 2], next_w=self.blocks[i + 1]["norm1"], h_out=h, w_offset=off)
+            # the layer's last residual sum rides in the depth average's launch (all rows, each once); the last layer's stays a launch of
+            # its own because the final average runs on the wanted rows only
+            fuse = i + 1 < L
+            last_w = blk["norm2b"] if kind else blk["norm1b"]
+            if kind:
+                nsq.gate_norm_add(x, y, None, blk["norm1b"], None, eps, blk["norm2"], h, w_offset=off)
+                if kind == "dense":
+                    gu = nsq.linear(h, blk["w_gu"], blk["b_gu"])
+                    y = nsq.linear(nsq.glu_mul(gu, blk["ff"]), blk["w_down"], blk["b_down"])
+                else:
+                    y = self._moe(h, blk)
+            if fuse:
+                nsq.depth_mix(xs, i + 2, blk["depth"], eps, x_out=xs[i + 2], next_w=self.blocks[i + 1]["norm1"], h_out=h, w_offset=off, y=y, y_w=last_w)
+            else:
+                nsq.gate_norm_add(x, y, None, last_w, None, eps, w_offset=off)
+            if fuse:
                 if self.layer_trace is not None:
                     self.layer_trace.append(xs[i + 2].clone())
         if self.layer_trace is not None and L:

@@ -83,6 +83,18 @@ def test_depth_average_and_norms_around_zero(nsq, width):
     hr = torch.empty(3, width, device=DEV)
     nsq.depth_mix(dev(xs), n, dev(a), 1e-5, next_w=dev(w), h_out=hr, w_offset=1.0, rows=rows)
     close(hr, O.norm_around_zero(want[[7, 0, 3]], w, 1e-5), 2e-6, "only the wanted rows")
+    # a sublayer's residual sum riding in the same launch: the newest term is updated in place first
+    yv, w3 = torch.randn(T, width, generator=g, dtype=F64), torch.randn(width, generator=g, dtype=F64) * 0.3
+    for ydt, wdt in ((F32, F32), (BF16, BF16), (F32, BF16)):
+        xs2 = dev(xs)
+        xo2, h2 = torch.empty(T, width, device=DEV), torch.empty(T, width, device=DEV, dtype=wdt)
+        nsq.depth_mix(xs2, n, dev(a), 1e-5, x_out=xo2, next_w=dev(w, wdt), h_out=h2, w_offset=1.0, y=dev(yv, ydt), y_w=dev(w3, wdt))
+        newest = xs[n - 1] + O.norm_around_zero(yv.to(ydt).to(F64), w3.to(wdt).to(F64), 1e-5)
+        want2 = sum(a[j] * xs[j] for j in range(n - 1)) + a[n - 1] * newest
+        close(xs2[n - 1], newest, 2e-6, "newest term after its residual sum")
+        close(xs2[:n - 1], xs[:n - 1].to(F32), 0, "older terms untouched")
+        close(xo2, want2, 3e-6, "average over the updated term")
+        close(h2, O.norm_around_zero(want2, w.to(wdt).to(F64), 1e-5), 2e-6 if wdt == F32 else 6e-3, "norm of it")
     # the sublayer's output norm, the residual sum and the next input norm, with the 1 added in 32-bit
     x, y, w2 = torch.randn(T, width, generator=g, dtype=F64), torch.randn(T, width, generator=g, dtype=F64), torch.randn(width, generator=g, dtype=F64) * 0.3
     for ydt in (F32, BF16):
