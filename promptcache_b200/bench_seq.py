@@ -395,7 +395,7 @@ def safilorn_config(s: dict) -> dict:
     moe = {"kind": "moe", "expert": {"ff": s["eff"], "limit": 7.0}, "router": {"experts": s["E"], "top": s["top"]}}
     att = lambda mlp: {"type": "latent_attention", "mlp": mlp,
                        "mixer": {"heads": s["H"], "dim": s["D"], "rot_dim": s["R"], "vdim": s["V"], "kv_rank": s["C"], "q_rank": s["Q"], "scale": (s["D"] + s["R"]) ** -0.5,
-                                 "rot": {"base": 10000.0, "dims": s["R"], "scaling": {"factor": 8.0, "original": 4096, "fast": 32.0, "slow": 1.0}}}}
+                                 "rot": {"base": 10000.0, "dims": s["R"], "scaling": {"factor": 8.0, "original": 4096, "fast": 24.0, "slow": 1.5}}}}
     rec = lambda mlp: {"type": "gla", "mixer": {"heads": s["mH"], "dim": s["mD"], "vdim": s["mV"], "tau": s["tau"]}, "mlp": mlp}
     return {"architecture": "Safilorn", "vocab": s["vocab"], "width": s["width"], "embedding": {"scale": 1.0}, "norm": {"eps": 1e-5},
             "layers": [rec(dense), att(moe), att(dense), rec(moe)] * s["repeat"]}

@@ -254,7 +254,9 @@ class SafilornForCausalLM(SlotPoolCausalLM):
         idx, wgt, _ = nsq.moe_route(h, blk["w_router"], None, None, blk["top"], bias=blk["b_router"], renorm=True)
         mode = self.moe_grouped
         if mode is None and torch.cuda.is_current_stream_capturing():
-            mode = False if T * blk["top"] <= 256 else "own"   # a recorded decoding step keeps to this library's own kernels
+            # a recorded decoding step keeps to this library's own kernels: the row kernels, or the grouped one where many pairs fit it
+            fits = self.compute_dtype == torch.bfloat16 and W % 8 == 0 and blk["we_down"].shape[2] % 8 == 0
+            mode = "own" if (T * blk["top"] > 256 and fits) else False
         ye, rows_e = nsq.moe_experts(h, idx, blk["we_gu"], blk["we_down"], grouped=mode, act=blk["act"])
         y = torch.empty(T, W, dtype=torch.float32, device=dev)
         nsq.moe_combine(y, ye, idx, wgt, h, blk["n_experts"], 1.0, y_row=rows_e, overwrite=True)
