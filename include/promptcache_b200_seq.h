@@ -34,6 +34,11 @@
  *   pcs_head_gate        out[t, h, :] = o[t, h, :] * sigmoid(g[t, h])
  *   pcs_gla_decay        per key channel log decay  logsigmoid(A2 a + b) / tau  of a gated linear-attention layer
  *   pcs_gla_scan         S_t = diag(alpha_t) S_(t-1) + k_t v_t^T, o_t = S_t^T q_t, per-head output norm and silu gate
+ *   pcs_add_layer_norm   residual sum of up to three sublayer results and layer norms (weight, no bias) of the new stream with
+ *                        one or two weight vectors, for layers whose sublayers run side by side on the same input
+ *   pcs_gru_scan         element-wise gated recurrence whose gates read only the current token, S_t = (1 - z_t) S_(t-1) + z_t c_t,
+ *                        with its silu output gate
+ *   (pcs_attn with `talk`: every (query, key) pair's scores of all heads are mixed by an [H, H] matrix before the softmax)
  *
  * All tensor arguments are DEVICE pointers; `dtype` selects the compute / storage type of activations, weights and K/V
  * rows: PCS_BF16 or PCS_F32 (true 32-bit everywhere).  The residual stream, norms' statistics, attention scores and
@@ -54,7 +59,7 @@
 extern "C" {
 #endif
 
-#define PCS_ABI_VERSION 3
+#define PCS_ABI_VERSION 4
 #define PCS_BF16 0
 #define PCS_F32 1
 
@@ -148,6 +153,11 @@ typedef struct pcs_attn_params {
                                leading part of the key rows themselves (v_pool == k_pool, v_row_stride == dim) */
   const float* sink_logit;  /* [H] or NULL */
   const int32_t* pool_slot; /* [n_seqs] or NULL: overrides seq_slot (a dense pool that is indexed by the batch entry) */
+  const float* talk;        /* [H, H] or NULL: the scaled scores of a (query, key) pair are mixed across heads before the mask and
+                               the softmax, score'[h] = sum_g talk[h, g] * score[g].  Not with a bias, a cap or a sink. */
+  const void* out_gate;     /* [n_tokens, out_gate_stride] `dtype` or NULL: out[t, c] *= sigmoid(out_gate[t, c]) over all H * vdim columns
+                               (an element-wise output gate, applied where the result is normalised; only with `talk`) */
+  int64_t out_gate_stride;
 } pcs_attn_params;
 /* scratch the key split of pcs_attn needs for n_tokens tokens */
 int64_t pcs_attn_workspace_floats(int n_tokens, int n_heads, int vdim);
@@ -241,6 +251,8 @@ typedef struct pcs_rope_params {
   const int32_t* tok_pos;
   const int32_t* seq_slot;
   int32_t n_tokens, dtype;
+  const void* q_norm_w;     /* [dim] `dtype` or NULL: every query head is divided by sqrt(mean(q^2) + eps) and multiplied by this, */
+  const void* k_norm_w;     /* [dim] or NULL: the same for every key head; both before the rotation, in 32-bit */
 } pcs_rope_params;
 int pcs_rope_kv_prep(const pcs_rope_params* p, void* stream);
 
@@ -261,6 +273,10 @@ typedef struct pcs_route_params {
   int32_t dtype;
   int32_t renorm;           /* 1: wgt is divided by the sum over the token's choices (the softmax over the chosen logits alone) */
   const float* bias;        /* [n_outputs] or NULL: added to z before the softmax */
+  int32_t score_fn;         /* 0: s = softmax(z) over all outputs; 1: s = sigmoid(z), every output by itself */
+  int32_t group_best;       /* a group's score is the sum of its group_best largest choice scores (0 or 1: its largest) */
+  float wgt_scale;          /* every weight is multiplied by this at the end (0 counts as 1) */
+  float renorm_eps;         /* with renorm: wgt / (sum + renorm_eps) */
 } pcs_route_params;
 int pcs_moe_route(const pcs_route_params* p, void* stream);
 
@@ -268,6 +284,11 @@ int pcs_moe_route(const pcs_route_params* p, void* stream);
  * u' = clamp(u, -limit, limit), g' * sigmoid(alpha * g') * (u' + 1).  A NULL pointer means PCS_GLU_SILU. */
 #define PCS_GLU_SILU 0
 #define PCS_GLU_CLAMPED_SWISH 1
+/* Activations of a feed-forward WITHOUT a gate branch (one up-projection): the weights are [n_experts, ff, width], a "gu" matrix
+ * holds ff columns, and the second argument of the activation does not exist.
+ *   PCS_ACT_RELU2     max(z, 0)^2            PCS_ACT_GELU_ERF   z/2 * (1 + erf(z / sqrt 2)) */
+#define PCS_ACT_RELU2 2
+#define PCS_ACT_GELU_ERF 3
 typedef struct pcs_glu_act {
   int32_t kind;
   float alpha, limit;
@@ -442,6 +463,48 @@ typedef struct pcs_gla_params {
   float* o_raw;             /* fp32 scratch [n_tokens, heads * vdim] */
 } pcs_gla_params;
 int pcs_gla_scan(const pcs_gla_params* p, void* stream);
+
+/* Residual sum and layer norm (weight, no bias) of the 32-bit stream.  Per row r (row(r) = rows ? rows[r] : r):
+ *   x[row, :] += sum_i y_mult[i] * y[i][row, :]          (n_addends <= 3 sublayer results, `dtype` or fp32; not with `rows`)
+ *   mu = mean(x[row]), var = mean((x[row] - mu)^2)        (two passes over the row, 32-bit)
+ *   h1[r, :] = (x[row] - mu) / sqrt(var + eps) * w1;  h2[r, :] likewise with w2   (each may be NULL) */
+typedef struct pcs_addln_params {
+  float* x;                 /* [*, width] */
+  const int32_t* rows;      /* [n_rows] or NULL */
+  const void* y[3];
+  int64_t y_stride[3];
+  float y_mult[3];
+  int32_t y_f32[3];
+  int32_t n_addends;
+  const void* w1;           /* [width] `dtype` */
+  void* h1;                 /* [n_rows, width] `dtype` */
+  const void* w2;
+  void* h2;
+  int32_t n_rows, width;
+  float eps;
+  int32_t dtype;
+} pcs_addln_params;
+int pcs_add_layer_norm(const pcs_addln_params* p, void* stream);
+
+/* Element-wise gated recurrence whose gates read only the current token (no dependence on the state).  Per entry and channel c:
+ *   z_t = sigmoid(proj[t, z_off + c]),  u_t = proj[t, x_off + c],  cand_t = u_t >= 0 ? u_t + 1/2 : sigmoid(u_t)
+ *   S_t = (1 - z_t) S_(t-1) + z_t cand_t                         (32-bit; an entry whose slot holds no tokens starts from zero)
+ *   out[t, c] = S_t * silu(proj[t, g_off + c])
+ * A block takes 32 channels of one entry; the entry's tokens are cut into segments that are scanned side by side (each as the
+ * pair (product of 1 - z, sum) of an affine map), joined in order, and scanned again from their true starts. */
+typedef struct pcs_gru_params {
+  const void* proj;         /* [n_tokens, row_stride] `dtype`, biases already added */
+  int64_t row_stride;
+  int32_t z_off, x_off, g_off, width;
+  void* out;                /* [n_tokens, width] `dtype` */
+  float* s_pool;            /* [slots, width] */
+  const int32_t* seq_slot;
+  const int32_t* seq_pos0;
+  const int32_t* seq_len;
+  const int32_t* seq_off;
+  int32_t n_seqs, n_tokens, max_len, dtype;
+} pcs_gru_params;
+int pcs_gru_scan(const pcs_gru_params* p, void* stream);
 
 /* The same recurrence in chunks of `chunk` tokens (prompts).  The step's entries are cut into chunks (an entry's last one may
  * be short); chunk c holds tokens chunk_first[c] .. chunk_first[c] + chunk_len[c] - 1 of the concatenated matrix.  With B_i the

@@ -19,8 +19,11 @@ PCS_BF16, PCS_F32 = 0, 1
 EXPORTS = ("pcs_version", "pcs_last_error", "pcs_launch_count", "pcs_attn_workspace_floats", "pcs_embed", "pcs_rmsnorm", "pcs_gate_norm_add", "pcs_xielu", "pcs_linear_rows",
            "pcs_qk_prep", "pcs_attn", "pcs_mlstm_gates", "pcs_mlstm_scan", "pcs_embed_bigram", "pcs_norm_conv", "pcs_rope_kv_prep", "pcs_moe_route",
            "pcs_moe_rows_up", "pcs_moe_rows_down", "pcs_moe_plan", "pcs_moe_gather", "pcs_moe_gemm", "pcs_moe_combine", "pcs_silu_mul", "pcs_glu_mul",
-           "pcs_depth_mix", "pcs_latent_prep", "pcs_latent_q", "pcs_latent_gather", "pcs_latent_expand", "pcs_head_gate", "pcs_gla_decay", "pcs_gla_scan", "pcs_gla_chunk_prep", "pcs_gla_chunk_scan", "pcs_gla_chunk_out")
+           "pcs_depth_mix", "pcs_latent_prep", "pcs_latent_q", "pcs_latent_gather", "pcs_latent_expand", "pcs_head_gate", "pcs_gla_decay", "pcs_gla_scan", "pcs_gla_chunk_prep", "pcs_gla_chunk_scan", "pcs_gla_chunk_out",
+           "pcs_add_layer_norm", "pcs_gru_scan")
 GLU_SILU, GLU_CLAMPED_SWISH = 0, 1
+ACT_RELU2, ACT_GELU_ERF = 2, 3          # activations of a feed-forward without a gate branch
+ROUTE_SOFTMAX, ROUTE_SIGMOID = 0, 1
 
 
 class pcs_gna_params(C.Structure):
@@ -50,7 +53,8 @@ class pcs_attn_params(C.Structure):
                 ("n_tokens", C.c_int32), ("n_seqs", C.c_int32), ("max_len", C.c_int32), ("dtype", C.c_int32),
                 ("impl", C.c_int32), ("max_keys", C.c_int32), ("workspace", C.c_void_p), ("workspace_floats", C.c_int64),
                 ("softcap", C.c_float), ("window", C.c_int32), ("keep_first", C.c_int32), ("v_row_stride", C.c_int32),
-                ("sink_logit", C.c_void_p), ("pool_slot", C.c_void_p)]
+                ("sink_logit", C.c_void_p), ("pool_slot", C.c_void_p), ("talk", C.c_void_p),
+                ("out_gate", C.c_void_p), ("out_gate_stride", C.c_int64)]
 
 
 class pcs_normconv_params(C.Structure):
@@ -65,14 +69,16 @@ class pcs_rope_params(C.Structure):
                 ("n_heads", C.c_int32), ("n_kv_heads", C.c_int32), ("dim", C.c_int32), ("vdim", C.c_int32),
                 ("freqs", C.c_void_p), ("rot_dims", C.c_int32), ("interleaved", C.c_int32), ("v_unit_rms", C.c_int32), ("eps", C.c_float),
                 ("q_out", C.c_void_p), ("k_pool", C.c_void_p), ("v_pool", C.c_void_p), ("cap", C.c_int32),
-                ("tok_seq", C.c_void_p), ("tok_pos", C.c_void_p), ("seq_slot", C.c_void_p), ("n_tokens", C.c_int32), ("dtype", C.c_int32)]
+                ("tok_seq", C.c_void_p), ("tok_pos", C.c_void_p), ("seq_slot", C.c_void_p), ("n_tokens", C.c_int32), ("dtype", C.c_int32),
+                ("q_norm_w", C.c_void_p), ("k_norm_w", C.c_void_p)]
 
 
 class pcs_route_params(C.Structure):
     _fields_ = [("h", C.c_void_p), ("h_stride", C.c_int64), ("w_router", C.c_void_p), ("correction", C.c_void_p), ("w_sg", C.c_void_p),
                 ("n_tokens", C.c_int32), ("width", C.c_int32), ("n_outputs", C.c_int32), ("top", C.c_int32), ("n_groups", C.c_int32),
                 ("keep_groups", C.c_int32), ("idx", C.c_void_p), ("wgt", C.c_void_p), ("shared_gate", C.c_void_p),
-                ("dtype", C.c_int32), ("renorm", C.c_int32), ("bias", C.c_void_p)]
+                ("dtype", C.c_int32), ("renorm", C.c_int32), ("bias", C.c_void_p),
+                ("score_fn", C.c_int32), ("group_best", C.c_int32), ("wgt_scale", C.c_float), ("renorm_eps", C.c_float)]
 
 
 class pcs_glu_act(C.Structure):
@@ -128,6 +134,18 @@ class pcs_combine_params(C.Structure):
                 ("ys", C.c_void_p), ("ys_stride", C.c_int64), ("shared_gate", C.c_void_p), ("mult", C.c_float),
                 ("n_tokens", C.c_int32), ("width", C.c_int32), ("top", C.c_int32), ("n_experts", C.c_int32), ("dtype", C.c_int32),
                 ("y_dtype", C.c_int32), ("y_row", C.c_void_p), ("overwrite", C.c_int32)]
+
+
+class pcs_addln_params(C.Structure):
+    _fields_ = [("x", C.c_void_p), ("rows", C.c_void_p), ("y", C.c_void_p * 3), ("y_stride", C.c_int64 * 3), ("y_mult", C.c_float * 3),
+                ("y_f32", C.c_int32 * 3), ("n_addends", C.c_int32), ("w1", C.c_void_p), ("h1", C.c_void_p), ("w2", C.c_void_p), ("h2", C.c_void_p),
+                ("n_rows", C.c_int32), ("width", C.c_int32), ("eps", C.c_float), ("dtype", C.c_int32)]
+
+
+class pcs_gru_params(C.Structure):
+    _fields_ = [("proj", C.c_void_p), ("row_stride", C.c_int64), ("z_off", C.c_int32), ("x_off", C.c_int32), ("g_off", C.c_int32), ("width", C.c_int32),
+                ("out", C.c_void_p), ("s_pool", C.c_void_p), ("seq_slot", C.c_void_p), ("seq_pos0", C.c_void_p), ("seq_len", C.c_void_p),
+                ("seq_off", C.c_void_p), ("n_seqs", C.c_int32), ("n_tokens", C.c_int32), ("max_len", C.c_int32), ("dtype", C.c_int32)]
 
 
 class pcs_mlstm_params(C.Structure):
@@ -202,6 +220,8 @@ def load() -> C.CDLL:
     lib.pcs_gla_scan.argtypes = [C.POINTER(pcs_gla_params), C.c_void_p]
     for name in ("pcs_gla_chunk_prep", "pcs_gla_chunk_scan", "pcs_gla_chunk_out"):
         getattr(lib, name).argtypes = [C.POINTER(pcs_gla_chunk_params), C.c_void_p]
+    lib.pcs_add_layer_norm.argtypes = [C.POINTER(pcs_addln_params), C.c_void_p]
+    lib.pcs_gru_scan.argtypes = [C.POINTER(pcs_gru_params), C.c_void_p]
     for name in EXPORTS[4:]:
         getattr(lib, name).restype = C.c_int
     _lib = lib
@@ -371,15 +391,19 @@ def attention(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor, out: 
               r1: Optional[torch.Tensor], r2: Optional[torch.Tensor], sink: bool, batch: Batch, impl: int = 0,
               max_keys: int = 0, workspace: Optional[torch.Tensor] = None, softcap: float = 0.0, window: int = 0,
               keep_first: int = 0, sink_logit: Optional[torch.Tensor] = None, v_row_stride: int = 0,
-              pool_slot: Optional[torch.Tensor] = None) -> None:
+              pool_slot: Optional[torch.Tensor] = None, talk: Optional[torch.Tensor] = None, out_gate: Optional[torch.Tensor] = None) -> None:
     """q [T, H*dim], out [T, H*vdim]; causal over each entry's own slot rows; r1 / r2 float32 [H] or None.  With a float32
     `workspace` (attn_workspace) and `max_keys` (upper bound of the keys a token sees) few tokens over many keys are run
     as several splits of the keys that a second launch merges.  `softcap` > 0 caps the scaled score by softcap * tanh(s /
     softcap); `window` > 0 limits query i to keys j with i - j < window or j < keep_first.  `sink_logit` (float32 [H], with
     sink=True): the sink's term is exp(sink_logit[h]) instead of exp(0).  `v_row_stride` > 0: a key's value row starts that many
     elements after the previous key's (the values may be a leading part of the key rows: pass the key pool as v_pool too; vdim is
-    then out's width per head).  `pool_slot` (int32 [entries]) replaces the batch's slots."""
-    _cuda(q, k_pool, v_pool, out, r1, r2, sink_logit, pool_slot)
+    then out's width per head).  `pool_slot` (int32 [entries]) replaces the batch's slots.  `talk` (float32 [H, H]): every (query, key)
+    pair's scaled scores are mixed across heads, s'[h] = sum_g talk[h, g] s[g], before the mask and the softmax; with it, `out_gate`
+    ([T, H * vdim], row stride free): out *= sigmoid(out_gate), element by element."""
+    _cuda(q, k_pool, v_pool, out, r1, r2, sink_logit, pool_slot, talk)
+    if talk is not None and (talk.dtype != torch.float32 or tuple(talk.shape) != (n_heads, n_heads) or not talk.is_contiguous()):
+        raise NativeError("attention: talk must be contiguous float32 [H, H]")
     if sink_logit is not None and (sink_logit.dtype != torch.float32 or sink_logit.numel() != n_heads or not sink_logit.is_contiguous()):
         raise NativeError("attention: sink_logit must be float32 [H]")
     if pool_slot is not None and (pool_slot.dtype != torch.int32 or pool_slot.numel() != batch.n_seqs or not pool_slot.is_contiguous()):
@@ -395,7 +419,12 @@ def attention(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor, out: 
     p.q, p.k_pool, p.v_pool, p.out = q.data_ptr(), k_pool.data_ptr(), v_pool.data_ptr(), out.data_ptr()
     p.n_heads, p.n_kv_heads, p.dim, p.cap = n_heads, k_pool.shape[1], k_pool.shape[3], k_pool.shape[2]
     p.vdim = out.shape[1] // n_heads if v_row_stride else v_pool.shape[3]
-    p.v_row_stride, p.sink_logit, p.pool_slot = int(v_row_stride), _ptr(sink_logit), _ptr(pool_slot)
+    p.v_row_stride, p.sink_logit, p.pool_slot, p.talk = int(v_row_stride), _ptr(sink_logit), _ptr(pool_slot), _ptr(talk)
+    if out_gate is not None:
+        _cuda(out_gate)
+        if out_gate.dtype != dt or out_gate.dim() != 2 or out_gate.stride(1) != 1 or tuple(out_gate.shape) != tuple(out.shape):
+            raise NativeError("attention: out_gate must be [T, H * vdim] in the compute type with a contiguous inner dimension")
+        p.out_gate, p.out_gate_stride = out_gate.data_ptr(), out_gate.stride(0)
     p.scale, p.bias_r1, p.bias_r2, p.sink = float(scale), _ptr(r1), _ptr(r2), 1 if sink else 0
     p.tok_seq, p.tok_pos, p.seq_slot = batch.tok_seq.data_ptr(), batch.tok_pos.data_ptr(), batch.seq_slot.data_ptr()
     p.seq_pos0, p.seq_len, p.seq_off = batch.seq_pos0.data_ptr(), batch.seq_len.data_ptr(), batch.seq_off.data_ptr()
@@ -498,11 +527,15 @@ def norm_conv(x: torch.Tensor, g: Optional[torch.Tensor], eps: float, h_out: Opt
 
 def rope_kv_prep(qkv: torch.Tensor, offs, n_heads: int, n_kv_heads: int, dim: int, vdim: int, freqs: Optional[torch.Tensor], rot_dims: int,
                  interleaved: bool, v_unit_rms: bool, eps: float, q_out: torch.Tensor, k_pool: Optional[torch.Tensor],
-                 v_pool: Optional[torch.Tensor], batch: Batch) -> None:
+                 v_pool: Optional[torch.Tensor], batch: Batch, q_norm_w: Optional[torch.Tensor] = None, k_norm_w: Optional[torch.Tensor] = None) -> None:
     """qkv [T, *] with q / k / v at the column offsets `offs` (k and v offsets None: the layer appends no rows).  freqs: float64
-    [rot_dims / 2] on the device."""
-    _cuda(qkv, q_out, k_pool, v_pool, freqs)
+    [rot_dims / 2] on the device.  `q_norm_w` / `k_norm_w` ([dim], shared by the heads): every query / key head is first divided by
+    its root mean square (eps inside the root) and multiplied by the weight."""
+    _cuda(qkv, q_out, k_pool, v_pool, freqs, q_norm_w, k_norm_w)
     dt = qkv.dtype
+    for w in (q_norm_w, k_norm_w):
+        if w is not None and (w.dtype != dt or not w.is_contiguous() or w.numel() != dim):
+            raise NativeError("rope_kv_prep: a head norm's weight must be contiguous [dim] in the compute type")
     _rows2d(qkv, dt, "rope_kv_prep: qkv")
     if not q_out.is_contiguous() or q_out.dtype != dt:
         raise NativeError("rope_kv_prep: q_out must be contiguous in the compute type")
@@ -521,13 +554,17 @@ def rope_kv_prep(qkv: torch.Tensor, offs, n_heads: int, n_kv_heads: int, dim: in
         p.k_pool, p.v_pool, p.cap = k_pool.data_ptr(), v_pool.data_ptr(), k_pool.shape[2]
     p.tok_seq, p.tok_pos, p.seq_slot = batch.tok_seq.data_ptr(), batch.tok_pos.data_ptr(), batch.seq_slot.data_ptr()
     p.n_tokens, p.dtype = batch.n_tokens, dtype_code(dt)
+    p.q_norm_w, p.k_norm_w = _ptr(q_norm_w), _ptr(k_norm_w)
     _check(load().pcs_rope_kv_prep(C.byref(p), _stream()), "pcs_rope_kv_prep")
 
 
 def moe_route(h: torch.Tensor, w_router: torch.Tensor, correction: Optional[torch.Tensor], w_sg: Optional[torch.Tensor], top: int, n_groups: int = 1,
-              keep_groups: int = 1, bias: Optional[torch.Tensor] = None, renorm: bool = False):
+              keep_groups: int = 1, bias: Optional[torch.Tensor] = None, renorm: bool = False, score_fn: int = ROUTE_SOFTMAX, group_best: int = 1,
+              wgt_scale: float = 1.0, renorm_eps: float = 0.0):
     """(idx int32 [T, top], wgt float32 [T, top], shared gate float32 [T] or None).  `bias` (float32 [outputs]) is added to the
-    router's outputs; `renorm`: the weights are the softmax over the chosen outputs alone."""
+    router's outputs; `renorm`: the weights are divided by their sum (+ renorm_eps) over the chosen outputs.  `score_fn`: softmax over
+    all outputs or a sigmoid of each; `group_best`: a group's score is the sum of that many of its largest choice scores;
+    `wgt_scale` multiplies the weights at the end."""
     _cuda(h, w_router, correction, w_sg, bias)
     if bias is not None and (bias.dtype != torch.float32 or not bias.is_contiguous() or bias.numel() != w_router.shape[0]):
         raise NativeError("moe_route: bias must be float32 [outputs]")
@@ -548,6 +585,7 @@ def moe_route(h: torch.Tensor, w_router: torch.Tensor, correction: Optional[torc
     p.n_tokens, p.width, p.n_outputs, p.top, p.n_groups, p.keep_groups = T, h.shape[1], w_router.shape[0], int(top), int(n_groups), int(keep_groups)
     p.idx, p.wgt, p.shared_gate, p.dtype = idx.data_ptr(), wgt.data_ptr(), _ptr(sg), dtype_code(dt)
     p.renorm, p.bias = 1 if renorm else 0, _ptr(bias)
+    p.score_fn, p.group_best, p.wgt_scale, p.renorm_eps = int(score_fn), int(group_best), float(wgt_scale), float(renorm_eps)
     _check(load().pcs_moe_route(C.byref(p), _stream()), "pcs_moe_route")
     return idx, wgt, sg
 
@@ -574,12 +612,14 @@ def moe_experts(h: torch.Tensor, idx: torch.Tensor, w_gu: torch.Tensor, w_down: 
       grouped="own"       the same through this library's grouped tensor-core kernel (`pcs_moe_gemm`), activation in its
                           epilogue, y float32 by pair
     None chooses by size: the row kernels up to 64 pairs, otherwise the library's product (or this library's where torch has none).
-    `act`: None for silu(gate) * up, or (kind, alpha, limit) of the gated activation (GLU_CLAMPED_SWISH)."""
+    `act`: None for silu(gate) * up, or (kind, alpha, limit) of the gated activation (GLU_CLAMPED_SWISH).  With an activation that
+    has no gate branch (ACT_RELU2, ACT_GELU_ERF) w_gu is [E, ff, width] and the grouped product of this library is not offered."""
     _cuda(h, idx, w_gu, w_down)
     dt = h.dtype
     _rows2d(h, dt, "moe_experts: h")
     E, ff2, W = w_gu.shape
-    ff = ff2 // 2
+    gated = act is None or int(act[0]) in (GLU_SILU, GLU_CLAMPED_SWISH)
+    ff = ff2 // 2 if gated else ff2
     if w_gu.dtype != dt or w_down.dtype != dt or not (w_gu.is_contiguous() and w_down.is_contiguous()) or tuple(w_down.shape) != (E, W, ff) \
             or idx.dtype != torch.int32 or not idx.is_contiguous() or W != h.shape[1]:
         raise NativeError("moe_experts: weights [E, 2 ff, width] and [E, width, ff] in h's type, idx contiguous int32")
@@ -591,7 +631,7 @@ def moe_experts(h: torch.Tensor, idx: torch.Tensor, w_gu: torch.Tensor, w_down: 
         grouped = "own"
     if grouped is None:
         grouped = ("library" if has_library else "own") if (can_group and P > MOE_ROWS_MAX_PAIRS) else False
-    if grouped == "own" and not can_group and P <= 256:
+    if grouped == "own" and ((not can_group and P <= 256) or not gated):
         grouped = False
     if grouped:
         if not can_group:
@@ -663,7 +703,8 @@ def silu_mul(gu: torch.Tensor, ff: int) -> torch.Tensor:
 
 
 def glu_mul(gu: torch.Tensor, ff: int, act=None) -> torch.Tensor:
-    """act(gu[:, :ff], gu[:, ff:2 ff]) with `act` None (silu(g) * u) or (kind, alpha, limit)."""
+    """act(gu[:, :ff], gu[:, ff:2 ff]) with `act` None (silu(g) * u) or (kind, alpha, limit); an activation without a gate branch
+    (ACT_RELU2, ACT_GELU_ERF) reads gu[:, :ff] alone."""
     _cuda(gu)
     _rows2d(gu, gu.dtype, "glu_mul: gu")
     out = torch.empty(gu.shape[0], ff, dtype=gu.dtype, device=gu.device)
@@ -879,3 +920,51 @@ def gla_scan(proj: torch.Tensor, offs, ld: torch.Tensor, norm_w: torch.Tensor, o
     o_raw = torch.empty(batch.n_tokens, H * V, dtype=torch.float32, device=proj.device)
     p.o_raw = o_raw.data_ptr()
     _check(load().pcs_gla_scan(C.byref(p), _stream()), "pcs_gla_scan")
+
+
+def add_layer_norm(x: torch.Tensor, addends, eps: float, w1: Optional[torch.Tensor] = None, h1: Optional[torch.Tensor] = None,
+                   w2: Optional[torch.Tensor] = None, h2: Optional[torch.Tensor] = None, rows: Optional[torch.Tensor] = None) -> None:
+    """x += sum_i mult_i * y_i for `addends` = [(y_i [T, width] in the compute type or float32, mult_i)] (at most three), then
+    h1 = ln(x) * w1 and h2 = ln(x) * w2 with ln(x) = (x - mean) / sqrt(var + eps) (each optional).  With `rows` (int32) only
+    those rows are normed (no addends) and h1 / h2 have one row per entry of `rows`."""
+    addends = list(addends or [])
+    _cuda(x, w1, h1, w2, h2, rows, *[y for y, _ in addends])
+    if x.dtype != torch.float32 or not x.is_contiguous() or x.dim() != 2 or len(addends) > 3:
+        raise NativeError("add_layer_norm: x must be a contiguous float32 matrix, with at most three addends")
+    wt = w1 if w1 is not None else w2
+    dt = wt.dtype if wt is not None else next((y.dtype for y, _ in addends if y.dtype != torch.float32), torch.float32)
+    R = rows.numel() if rows is not None else x.shape[0]
+    if rows is not None and (rows.dtype != torch.int32 or not rows.is_contiguous() or addends):
+        raise NativeError("add_layer_norm: rows must be contiguous int32, and a row subset takes no addends")
+    p = pcs_addln_params()
+    p.x, p.rows, p.n_addends = x.data_ptr(), _ptr(rows), len(addends)
+    for j, (y, mult) in enumerate(addends):
+        if y.dim() != 2 or y.stride(1) != 1 or tuple(y.shape) != tuple(x.shape) or y.dtype not in (torch.float32, dt):
+            raise NativeError("add_layer_norm: an addend must be [T, width] in the compute type or float32")
+        p.y[j], p.y_stride[j], p.y_mult[j], p.y_f32[j] = y.data_ptr(), y.stride(0), float(mult), 1 if (y.dtype == torch.float32 and dt != torch.float32) else 0
+    for w, h in ((w1, h1), (w2, h2)):
+        if w is not None and (h is None or w.dtype != dt or h.dtype != dt or not (w.is_contiguous() and h.is_contiguous()) or w.numel() != x.shape[1]
+                              or tuple(h.shape) != (R, x.shape[1])):
+            raise NativeError("add_layer_norm: a weight [width] needs its output [rows, width], both in the compute type")
+    p.w1, p.h1, p.w2, p.h2 = _ptr(w1), _ptr(h1) if w1 is not None else None, _ptr(w2), _ptr(h2) if w2 is not None else None
+    p.n_rows, p.width, p.eps, p.dtype = R, x.shape[1], float(eps), dtype_code(dt)
+    _check(load().pcs_add_layer_norm(C.byref(p), _stream()), "pcs_add_layer_norm")
+
+
+def gru_scan(proj: torch.Tensor, offs, width: int, out: torch.Tensor, s_pool: torch.Tensor, batch: Batch) -> None:
+    """proj [T, *] with the gate's pre-activation, the candidate's input and the output gate's pre-activation at the column offsets
+    `offs` = (z, x, g), `width` channels each; state pool float32 [slots, width]; out [T, width] = S_t * silu(g_t)."""
+    _cuda(proj, out, s_pool)
+    dt = proj.dtype
+    _rows2d(proj, dt, "gru_scan: proj")
+    if s_pool.dtype != torch.float32 or not s_pool.is_contiguous() or s_pool.dim() != 2 or s_pool.shape[1] != width or out.dtype != dt \
+            or not out.is_contiguous() or tuple(out.shape) != (proj.shape[0], width):
+        raise NativeError("gru_scan: the state pool must be contiguous float32 [slots, width], out contiguous [T, width] in the compute type")
+    p = pcs_gru_params()
+    p.proj, p.row_stride = proj.data_ptr(), proj.stride(0)
+    p.z_off, p.x_off, p.g_off = offs
+    p.width, p.out, p.s_pool = int(width), out.data_ptr(), s_pool.data_ptr()
+    p.seq_slot, p.seq_pos0, p.seq_len, p.seq_off = (batch.seq_slot.data_ptr(), batch.seq_pos0.data_ptr(), batch.seq_len.data_ptr(),
+                                                    batch.seq_off.data_ptr())
+    p.n_seqs, p.n_tokens, p.max_len, p.dtype = batch.n_seqs, batch.n_tokens, batch.max_len, dtype_code(dt)
+    _check(load().pcs_gru_scan(C.byref(p), _stream()), "pcs_gru_scan")

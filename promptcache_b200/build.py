@@ -22,7 +22,7 @@ HEADERS = [os.path.join(CSRC, "pc_common.cuh"), os.path.join(CSRC, "linear_commo
 SEQ_LIB = os.path.join(HERE, "libpromptcache_b200_seq.so")
 SEQ_STAMP = os.path.join(HERE, ".libpromptcache_b200_seq.stamp")
 SEQ_SOURCES = ["seq_norms.cu", "seq_attn.cu", "seq_attn_tc.cu", "seq_mlstm.cu", "seq_mlstm_chunk.cu", "seq_linear.cu", "seq_canon.cu", "seq_rope.cu", "seq_moe.cu", "seq_moe_gemm.cu",
-               "seq_gla.cu", "seq_latent.cu", "seq_attn_latent.cu"]
+               "seq_gla.cu", "seq_latent.cu", "seq_attn_latent.cu", "seq_layernorm.cu", "seq_gru.cu", "seq_attn_talk.cu", "seq_attn_talk_tc.cu"]
 SEQ_HEADERS = [os.path.join(CSRC, "seq_common.cuh"), os.path.join(CSRC, "seq_mma.cuh"), os.path.join(HERE, "..", "include", "promptcache_b200_seq.h")]
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-O3", "-std=c++17", "-lineinfo",
               "-Xcompiler", "-fPIC", "-Xcompiler", "-fvisibility=hidden", "--expt-relaxed-constexpr"]

@@ -442,7 +442,9 @@ __global__ void __launch_bounds__(kAttnThreads) attn_combine_kernel(const pcs_at
 #pragma unroll
     for (int s = 0; s < kAttnMaxSplits; ++s)
       if (s < S) a = fmaf(v[s], fs[s], a);
-    stf(o + c, a * inv);
+    a *= inv;
+    if (p.out_gate) a *= sigmoidf_(ldf(static_cast<const T*>(p.out_gate) + static_cast<long long>(t) * p.out_gate_stride + h * V + c));
+    stf(o + c, a);
   }
 }
 
@@ -478,6 +480,7 @@ PCS_API int pcs_qk_prep(const pcs_qkprep_params* p, void* stream) {
 namespace pcs {
 int launch_attn_tc(const pcs_attn_params& p, cudaStream_t st, bool* handled);
 int launch_attn_latent(const pcs_attn_params& p, cudaStream_t st, int* splits_out);
+int launch_attn_talk(const pcs_attn_params& p, cudaStream_t st, int* splits_out);
 }
 
 PCS_API int pcs_attn(const pcs_attn_params* p, void* stream) {
@@ -491,7 +494,18 @@ PCS_API int pcs_attn(const pcs_attn_params* p, void* stream) {
   PCS_REQUIRE(p->n_heads <= 65535, "pcs_attn: too many heads");
   PCS_REQUIRE((p->bias_r1 == nullptr) == (p->bias_r2 == nullptr), "pcs_attn: the distance bias needs both r1 and r2");
   PCS_REQUIRE(p->v_row_stride == 0 || p->v_row_stride >= p->vdim, "pcs_attn: the value row stride %d is below vdim %d", p->v_row_stride, p->vdim);
+  PCS_REQUIRE(p->out_gate == nullptr || p->talk != nullptr, "pcs_attn: the element-wise output gate comes with mixed head scores only");
   cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (p->talk) {  // scores mixed across heads: kernels of their own (a block needs all heads of a pair), the same split merge
+    int talk_splits = 1;
+    if (int rc = pcs::launch_attn_talk(*p, st, &talk_splits)) return rc;
+    if (talk_splits > 1) {
+      PCS_DISPATCH(p->dtype, pcs::attn_combine_kernel<T><<<dim3(p->n_tokens, p->n_heads, (p->vdim + pcs::kAttnThreads - 1) / pcs::kAttnThreads), pcs::kAttnThreads, 0, st>>>(*p, talk_splits));
+      PCS_CHECK_CUDA(cudaGetLastError());
+      pcs::count_launch();
+    }
+    return PCS_OK;
+  }
   if (p->impl == 0) {  // (impl 2: the plain kernels with the split of the keys, never a tensor-core kernel)
     bool handled = false;
     if (int rc = pcs::launch_attn_tc(*p, st, &handled)) return rc;

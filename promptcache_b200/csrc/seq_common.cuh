@@ -134,12 +134,19 @@ __device__ __forceinline__ void angle_sincos(int pos, double f, float* s, float*
 
 // The gated activation of a feed-forward, by value (a kernel argument): PCS_GLU_SILU: silu(g) * u;
 // PCS_GLU_CLAMPED_SWISH: g' = min(g, limit), u' = clamp(u, -limit, limit), g' * sigmoid(alpha * g') * (u' + 1).
+// PCS_ACT_RELU2 and PCS_ACT_GELU_ERF have no gate branch (`gated()` is false): the first argument alone is used.
 struct GluAct {
   int kind;
   float alpha, limit;
   __host__ GluAct() : kind(PCS_GLU_SILU), alpha(1.f), limit(0.f) {}
   __host__ explicit GluAct(const pcs_glu_act* a) : kind(a ? a->kind : PCS_GLU_SILU), alpha(a ? a->alpha : 1.f), limit(a ? a->limit : 0.f) {}
+  __host__ __device__ __forceinline__ bool gated() const { return kind == PCS_GLU_SILU || kind == PCS_GLU_CLAMPED_SWISH; }
   __device__ __forceinline__ float operator()(float g, float u) const {
+    if (kind == PCS_ACT_RELU2) {
+      const float r = fmaxf(g, 0.f);
+      return r * r;
+    }
+    if (kind == PCS_ACT_GELU_ERF) return 0.5f * g * (1.f + erff(g * 0.70710678118654752440f));
     if (kind == PCS_GLU_CLAMPED_SWISH) {
       g = fminf(g, limit);
       u = fminf(fmaxf(u, -limit), limit);

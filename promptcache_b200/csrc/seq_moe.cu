@@ -1,9 +1,10 @@
 // Mixture of experts: the router, the chosen experts for a handful of rows, and the weighted sum into the residual stream.
 //
 // pcs_moe_route      one block per token.  Warps share the router's outputs (a 32-bit dot product each, lanes over K), then
-//                    warp 0 alone does the rest in shared memory: softmax over all outputs, choice scores (score +
-//                    correction), the groups' best choice scores, the best groups, and `top` rounds of an arg-max whose ties go
-//                    to the lower index.  The weights handed on are the plain softmax scores.  A second dot product gives the
+//                    warp 0 alone does the rest in shared memory: softmax over all outputs (or a sigmoid of each), choice scores
+//                    (score + correction), the groups' scores (their best choice score, or the sum of their few best), the best
+//                    groups, and `top` rounds of an arg-max whose ties go to the lower index.  The weights handed on are the plain
+//                    scores, optionally over the sum of the chosen ones and times a constant.  A second dot product gives the
 //                    shared expert's gate.  Every sum has an order that depends on the sizes alone.
 // pcs_moe_rows_up    block = (pair, 8 features): a warp owns two features, its lanes share K in 16-byte pieces with the gate
 // pcs_moe_rows_down  and up rows of both features in flight; the expert's weights are read once per pair.  Any number of
@@ -77,23 +78,50 @@ __device__ __forceinline__ void route_select(const pcs_route_params& p, int t, i
   if (p.bias) {
     for (int e = lane; e < E; e += 32) z[e] += p.bias[e];
   }
-  for (int e = lane; e < E; e += 32) m = fmaxf(m, z[e]);
-  m = warp_max(m);
-  float sum = 0.f;
-  for (int e = lane; e < E; e += 32) { const float w = expf(z[e] - m); z[e] = w; sum += w; }
-  sum = warp_sum(sum);
-  const float inv = 1.f / sum;
-  for (int e = lane; e < E; e += 32) {
-    const float s = z[e] * inv;
-    z[e] = s;
-    c[e] = s + (p.correction ? p.correction[e] : 0.f);
+  if (p.score_fn == 1) {  // every output's own sigmoid
+    for (int e = lane; e < E; e += 32) {
+      const float s = sigmoidf_(z[e]);
+      z[e] = s;
+      c[e] = s + (p.correction ? p.correction[e] : 0.f);
+    }
+  } else {
+    for (int e = lane; e < E; e += 32) m = fmaxf(m, z[e]);
+    m = warp_max(m);
+    float sum = 0.f;
+    for (int e = lane; e < E; e += 32) { const float w = expf(z[e] - m); z[e] = w; sum += w; }
+    sum = warp_sum(sum);
+    const float inv = 1.f / sum;
+    for (int e = lane; e < E; e += 32) {
+      const float s = z[e] * inv;
+      z[e] = s;
+      c[e] = s + (p.correction ? p.correction[e] : 0.f);
+    }
   }
   __syncwarp();
   const int G = p.n_groups, per = E / G;
   if (G > 1 && p.keep_groups < G) {
+    const int nb = min(max(p.group_best, 1), per);
     for (int g = lane; g < G; g += 32) {
       float b = -INFINITY;
-      for (int e = g * per; e < (g + 1) * per; ++e) b = fmaxf(b, c[e]);
+      if (nb == 1) {
+        for (int e = g * per; e < (g + 1) * per; ++e) b = fmaxf(b, c[e]);
+      } else {  // the sum of the group's nb largest choice scores: nb rounds over the group, each below the last one taken
+        float sum_b = 0.f, last = INFINITY;
+        int last_e = -1;
+        for (int r = 0; r < nb; ++r) {
+          float bv = -INFINITY;
+          int be = -1;
+          for (int e = g * per; e < (g + 1) * per; ++e) {
+            const float v = c[e];
+            const bool free_e = v < last || (v == last && e > last_e);   // not taken by an earlier round (ties go by index)
+            if (free_e && (v > bv || be < 0)) { bv = v; be = e; }
+          }
+          sum_b += bv;
+          last = bv;
+          last_e = be;
+        }
+        b = sum_b;
+      }
       gs[g] = b;
       gs[G + g] = 0.f;
     }
@@ -128,8 +156,12 @@ __device__ __forceinline__ void route_select(const pcs_route_params& p, int t, i
     float* w = p.wgt + static_cast<long long>(t) * p.top;
     float sum_k = 0.f;
     for (int k = 0; k < p.top; ++k) sum_k += w[k];
-    const float inv_k = 1.f / sum_k;
+    const float inv_k = 1.f / (sum_k + p.renorm_eps);
     for (int k = 0; k < p.top; ++k) w[k] *= inv_k;
+  }
+  if (p.wgt_scale != 0.f && p.wgt_scale != 1.f && lane == 0) {
+    float* w = p.wgt + static_cast<long long>(t) * p.top;
+    for (int k = 0; k < p.top; ++k) w[k] *= p.wgt_scale;
   }
 }
 
@@ -193,14 +225,15 @@ __global__ void __launch_bounds__(128) moe_rows_up_kernel(const T* __restrict__ 
   if (e >= n_experts || e < 0) return;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const T* x = h + static_cast<long long>(pr / top) * h_stride;
-  const T* wg = w_gu + static_cast<long long>(e) * 2 * ff * K;
+  const bool gated = glu.gated();   // without a gate branch an expert has ff rows, not 2 ff
+  const T* wg = w_gu + static_cast<long long>(e) * (gated ? 2 : 1) * ff * K;
   const T* wu = wg + static_cast<long long>(ff) * K;
 #pragma unroll
   for (int u = 0; u < 2; ++u) {
     const int n = blockIdx.y * 8 + warp * 2 + u;
     if (n >= ff) return;
     const float g = warp_dot(x, wg + static_cast<long long>(n) * K, K, lane, vec);
-    const float v = warp_dot(x, wu + static_cast<long long>(n) * K, K, lane, vec);
+    const float v = gated ? warp_dot(x, wu + static_cast<long long>(n) * K, K, lane, vec) : 0.f;
     if (lane == 0) stf(act + static_cast<long long>(pr) * ff + n, glu(g, v));
   }
 }
@@ -292,19 +325,20 @@ __global__ void __launch_bounds__(256) silu_mul_kernel(const T* __restrict__ gu,
   const int r = blockIdx.x;
   const T* g = gu + r * gu_stride;
   T* o = out + static_cast<long long>(r) * ff;
+  const bool gated = glu.gated();
   if (VEC) {
     for (int i = (blockIdx.y * 256 + threadIdx.x) * N; i < ff; i += gridDim.y * 256 * N) {
       float a[N], u[N];
       ld16(g + i, a);
-      ld16(g + ff + i, u);
+      if (gated) ld16(g + ff + i, u);
 #pragma unroll
-      for (int e = 0; e < N; ++e) a[e] = glu(a[e], u[e]);
+      for (int e = 0; e < N; ++e) a[e] = glu(a[e], gated ? u[e] : 0.f);
       st16(o + i, a);
     }
   } else {
     for (int i = blockIdx.y * 256 + threadIdx.x; i < ff; i += gridDim.y * 256) {
       const float a = ldf(g + i);
-      stf(o + i, glu(a, ldf(g + ff + i)));
+      stf(o + i, glu(a, gated ? ldf(g + ff + i) : 0.f));
     }
   }
 }
@@ -386,7 +420,7 @@ PCS_API int pcs_silu_mul(const void* gu, int64_t gu_stride, void* out, int n_row
 PCS_API int pcs_glu_mul(const void* gu, int64_t gu_stride, void* out, int n_rows, int ff, const pcs_glu_act* glu, int dtype, void* stream) {
   if (n_rows == 0 || ff == 0) return PCS_OK;
   PCS_REQUIRE(gu && out && n_rows > 0 && ff > 0, "pcs_glu_mul: bad arguments");
-  PCS_REQUIRE(glu == nullptr || glu->kind == PCS_GLU_SILU || glu->kind == PCS_GLU_CLAMPED_SWISH, "pcs_glu_mul: unknown activation %d", glu->kind);
+  PCS_REQUIRE(glu == nullptr || (glu->kind >= PCS_GLU_SILU && glu->kind <= PCS_ACT_GELU_ERF), "pcs_glu_mul: unknown activation %d", glu->kind);
   const pcs::GluAct act(glu);
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   const int piece = dtype == PCS_BF16 ? 8 : 4;

@@ -273,6 +273,7 @@ PCS_API int pcs_moe_gemm(int stage, const void* a, int64_t a_stride, const void*
   }
   PCS_REQUIRE(grid.y <= 65535, "pcs_moe_gemm: too many output features");
   const pcs::GluAct act(glu);
+  if (!act.gated()) return pcs::set_error(PCS_ERR_UNSUPPORTED, "pcs_moe_gemm: experts without a gate branch (activation %d) take the row kernels or the library's grouped product", act.kind);
   const __nv_bfloat16* ap = static_cast<const __nv_bfloat16*>(a);
   const __nv_bfloat16* wp = static_cast<const __nv_bfloat16*>(w);
   if (stage == 0) pcs::moe_gemm_kernel<0><<<grid, pcs::G_THREADS, pcs::G_SMEM, st>>>(ap, a_stride, wp, plan, out, n_pairs, top, n_experts, ff, width, act);

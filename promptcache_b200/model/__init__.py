@@ -258,11 +258,33 @@ class Safilorn(LanguageModel):
         raise NotImplementedError("Safilorn keeps recurrent state next to latent rows: there is no per-module K/V to cache and splice")
 
 
+class Tevilix(LanguageModel):
+    """Adapter of the Tevilix design (model/tevilix.py) for the generation engine.  Its recurrent branches carry a state from
+    token to token beside the attention branch's K/V rows, so a prompt's state cannot be cut at module boundaries and spliced:
+    pass `cache=None` to `GenerationEngine.generate`, or batch requests with `BatchEngine`."""
+
+    def __init__(self, name: str, model=None, tokenizer=None, **kwargs):
+        from .tevilix import TevilixForCausalLM
+        if model is None:
+            model = TevilixForCausalLM.from_pretrained(name, **kwargs)
+        if tokenizer is None:
+            from ..synthetic import IdTokenizer
+            tokenizer = IdTokenizer(model.vocab_size)
+        super().__init__(name, model, tokenizer, [tokenizer.eos_token_id], [])
+
+    def get_formatter(self) -> Callable[[str], str]:
+        return lambda prompt: prompt
+
+    def get_cache_shape(self) -> Tuple[int, int, int]:
+        raise NotImplementedError("Tevilix keeps recurrent state next to K/V rows: there is no per-module K/V to cache and splice")
+
+
 # config.json "architecture" (or transformers' "architectures"/"model_type") -> loader of the bare model
 MODEL_REGISTRY = {
     "Mutolix": lambda path, **kw: _mutolix(path, **kw),
     "Raritar": lambda path, **kw: _lazy("raritar", "RaritarForCausalLM").from_pretrained(path, **kw),
     "Safilorn": lambda path, **kw: _lazy("safilorn", "SafilornForCausalLM").from_pretrained(path, **kw),
+    "Tevilix": lambda path, **kw: _lazy("tevilix", "TevilixForCausalLM").from_pretrained(path, **kw),
     "LlamaForCausalLM": lambda path, dtype=None, **kw: LlamaForCausalLM.from_pretrained(path, **kw),
     "FalconForCausalLM": lambda path, dtype=None, **kw: _lazy("falcon", "FalconForCausalLM").from_pretrained(path, **kw),
     "MptForCausalLM": lambda path, dtype=None, **kw: _lazy("mpt", "MptForCausalLM").from_pretrained(path, **kw),
@@ -294,5 +316,5 @@ def load_model(path: str, device="cuda", dtype=None, **kwargs):
     return loader(path, device=device, **kwargs)
 
 
-__all__ = ["LanguageModel", "Mutolix", "Raritar", "Safilorn", "MODEL_REGISTRY", "load_model", "Llama2", "CodeLlama", "Falcon", "Mpt", "FormatConversation",
+__all__ = ["LanguageModel", "Mutolix", "Raritar", "Safilorn", "Tevilix", "MODEL_REGISTRY", "load_model", "Llama2", "CodeLlama", "Falcon", "Mpt", "FormatConversation",
            "FormatLlama2Conversation", "LlamaForCausalLM", "LlamaConfigLite"]

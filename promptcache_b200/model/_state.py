@@ -10,6 +10,7 @@ layer has pool tensors whose first dimension is the slot,
     decaying matrix   S [slots, H, dim, vdim]                                      (float32)
     matrix memory     S [slots, H, dim, vdim]    n [slots, H, dim]    m [slots, H]  (float32)
     short convolution tail [slots, 2, taps - 1, width]                             (float32, double-buffered)
+    vector state      vec [slots, width]                                            (float32)
 
 (a layer's spec may be a tuple of these, or None for a layer that reads another layer's rows)
 
@@ -66,6 +67,12 @@ class ConvTailSpec:
     width: int
 
 
+@dataclass(frozen=True)
+class VectorStateSpec:
+    """An element-wise recurrent layer's state: one number per channel."""
+    width: int
+
+
 class SlotPool:
     def __init__(self, specs: List[object], dtype: torch.dtype, device, n_slots: int = 2, cap: int = 128,
                  max_tokens: Optional[int] = None):
@@ -98,6 +105,8 @@ class SlotPool:
                     "v": torch.zeros(n_slots, spec.n_kv_heads, cap, spec.vdim, dtype=self.dtype, device=self.device)}
         if isinstance(spec, LatentKVSpec):
             return {"ckv": torch.zeros(n_slots, 1, cap, spec.rank + spec.rot_dim, dtype=self.dtype, device=self.device)}
+        if isinstance(spec, VectorStateSpec):
+            return {"vec": torch.zeros(n_slots, spec.width, dtype=torch.float32, device=self.device)}
         if isinstance(spec, DecayStateSpec):
             return {"s": torch.zeros(n_slots, spec.heads, spec.dim, spec.vdim, dtype=torch.float32, device=self.device)}
         if isinstance(spec, MatrixMemorySpec):
