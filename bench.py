@@ -559,14 +559,14 @@ def main():
     ap.add_argument("--layers", type=int, default=None, help="debug only: fewer layers (marks the line invalid)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-extras", action="store_true", help="skip the c5 / c4 / sweep / ablation blocks (headline only)")
-    ap.add_argument("--design", default=None, choices=["mutolix", "raritar", "safilorn"],
+    ap.add_argument("--design", default=None, choices=["mutolix", "raritar", "safilorn", "tevilix"],
                     help="instead of the headline workload: prefill / decode throughput and per-kernel rooflines of that design "
                          "beside the closest prompt-cache model at equal sizes (one GPU, one JSON line)")
     ap.add_argument("--profile", action="store_true",
                     help="after warm-up run ONE step between cudaProfilerStart/Stop and exit (for ncu --profile-from-start off)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "b200" else args.warmup
-    if args.design in ("mutolix", "raritar", "safilorn"):
+    if args.design in ("mutolix", "raritar", "safilorn", "tevilix"):
         from promptcache_b200 import bench_seq
         bench_seq.run(args, load_peaks, ClockSampler)
         return

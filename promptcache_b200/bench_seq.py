@@ -1,7 +1,8 @@
 """Throughput of the slot-pool designs beside the closest existing model at equal sizes: `bench.py --design mutolix`
 (against the Llama prompt-cache path), `bench.py --design raritar` (against Mutolix's attention layers with a dense
 feed-forward of the same active size, which share the step function, the pool and the attention kernels) and
-`bench.py --design safilorn` (against Mutolix with the same order and sizes of recurrent and attention layers).  Random weights, synthetic token ids.  Prefill and decode tokens/s of both models through their own
+`bench.py --design safilorn` (against Mutolix with the same order and sizes of recurrent and attention layers) and
+`bench.py --design tevilix` (against the same Mutolix model; its four layers run as a loop where Mutolix repeats them).  Random weights, synthetic token ids.  Prefill and decode tokens/s of both models through their own
 step / forward, then every kernel of the new design alone against its roofline, next to the like kernel of the Llama path.
 
 Timing: CUDA events on the launching stream, >= 3 warm-up iterations, a 256 MiB write between timed iterations (flushes the
@@ -598,7 +599,204 @@ def run_safilorn(args, load_peaks, ClockSampler) -> None:
     print(json.dumps(line), flush=True)
 
 
+TEVILIX_SIZES = {
+    # the recurrent and attention sizes of SIZES; a sliding window, a partly rotated head, the element-wise recurrence as wide as the model;
+    # the feed-forward alternates dense (ff) and experts without a gate branch (E of eff, `top` active: the same active size)
+    "w1024": dict(SIZES["w1024"], window=1024, rot=64, gru=1024, E=8, top=2, groups=(4, 2), eff=2048),
+    "w2048": dict(SIZES["w2048"], window=1024, rot=64, gru=2048, E=16, top=4, groups=(4, 2), eff=2048),
+}
+
+
+def tevilix_config(s: dict) -> dict:
+    dense = {"kind": "dense", "ff": s["ff"]}
+    moe = {"kind": "moe", "expert": {"ff": s["eff"]}, "router": {"experts": s["E"], "top": s["top"], "scale": 2.0, "groups": {"count": s["groups"][0], "keep": s["groups"][1]}}}
+    par = lambda mlp: {"type": "parallel", "mlp": mlp,
+                       "mixer": {"left": {"heads": s["H"], "kv_heads": s["G"], "dim": s["D"], "vdim": s["V"], "scale": s["D"] ** -0.5, "mask": {"size": s["window"]},
+                                          "rot": {"base": 10000.0, "dims": s["rot"], "scaling": {"factor": 8.0}}},
+                                 "left_scale": 0.7, "right": {"width": s["gru"]}, "right_scale": 0.8}}
+    rec = lambda mlp: {"type": "mlstm", "mixer": {"heads": s["mH"], "dim": s["mD"], "vdim": s["mV"], "gate_cap": 15.0}, "mlp": mlp}
+    # four layers; the wider size runs them `repeat` times as a loop where the model it is compared with has that many more layers
+    return {"architecture": "Tevilix", "vocab": s["vocab"], "width": s["width"], "embedding": {"scale": 1.0}, "norm": {"eps": 1e-5},
+            "loop": {"start": 0, "stop": 4, "times": s["repeat"]}, "layers": [rec(dense), par(moe), par(dense), rec(moe)]}
+
+
+def tevilix_tensors(cfg: dict, device, seed: int = 0) -> Dict[str, torch.Tensor]:
+    g = torch.Generator(device=device).manual_seed(seed)
+    W, t = cfg["width"], {}
+    rnd = lambda *shape, std=1.0, mean=0.0: (torch.randn(*shape, generator=g, device=device) * std + mean).to(torch.bfloat16)
+    lin = lambda o, i: rnd(o, i, std=i ** -0.5)
+    t["embed"], t["final.norm"], t["head"] = rnd(cfg["vocab"], W), rnd(W, std=0.05, mean=1.0), lin(cfg["vocab"], W)
+    for i, layer in enumerate(cfg["layers"]):
+        p, m, f = f"l{i}.", layer["mixer"], layer["mlp"]
+        t[p + "norm1"], t[p + "norm2"] = rnd(W, std=0.05, mean=1.0), rnd(W, std=0.05, mean=1.0)
+        if layer["type"] == "mlstm":
+            H, D, V = m["heads"], m["dim"], m["vdim"]
+            t[p + "mix.q"], t[p + "mix.k"], t[p + "mix.v"], t[p + "mix.g"] = lin(H * D, W), lin(H * D, W), lin(H * V, W), lin(H * V, W)
+            t[p + "mix.o"], t[p + "mix.norm"] = lin(W, H * V) * 0.3, rnd(H * V, std=0.05, mean=1.0)
+            t[p + "mix.i"], t[p + "mix.i.b"], t[p + "mix.f"], t[p + "mix.f.b"] = lin(H, W), rnd(H), lin(H, W), rnd(H, mean=3.0)
+        else:
+            a, q, r = m["left"], p + "mix.left.", p + "mix.right."
+            H, G, D, V, R = a["heads"], a["kv_heads"], a["dim"], a["vdim"], m["right"]["width"]
+            for n, rows in (("q", H * D), ("k", G * D), ("v", G * V)):
+                t[q + n], t[q + n + ".b"] = lin(rows, W), rnd(rows, std=0.1)
+            t[q + "q.norm"], t[q + "k.norm"] = rnd(D, std=0.1, mean=1.0), rnd(D, std=0.1, mean=1.0)
+            t[q + "talk"] = (torch.eye(H, device=device) + torch.randn(H, H, generator=g, device=device) * 0.2).to(torch.bfloat16)
+            t[q + "g"], t[q + "o"], t[q + "o.b"] = lin(H * V, W), lin(W, H * V) * 0.3, rnd(W, std=0.05)
+            t[r + "z"], t[r + "z.b"], t[r + "x"], t[r + "x.b"] = lin(R, W), rnd(R), lin(R, W), rnd(R, std=0.3)
+            t[r + "g"], t[r + "o"] = lin(R, W), lin(W, R) * 0.3
+        if f["kind"] == "dense":
+            t[p + "mlp.up"], t[p + "mlp.down"] = lin(f["ff"], W), lin(W, f["ff"]) * 0.3
+        else:
+            E, ff = f["router"]["experts"], f["expert"]["ff"]
+            t[p + "mlp.router"], t[p + "mlp.correction"] = rnd(E, W, std=3 * W ** -0.5), rnd(E, std=0.1)
+            for e in range(E):
+                t[f"{p}mlp.e{e}.up"], t[f"{p}mlp.e{e}.down"] = lin(ff, W), lin(W, ff) * 0.3
+    return t
+
+
+def tevilix_block(s: dict, dev, timer: Timer, prompt: int, batch: int, ctx: int) -> dict:
+    from .model.mutolix import MutolixConfig, MutolixForCausalLM
+    from .model.tevilix import TevilixConfig, TevilixForCausalLM
+    cfg = tevilix_config(s)
+    tc = TevilixConfig(cfg)
+    out = {"layers": len(cfg["layers"]), "layer_runs": len(tc.runs), "width": s["width"], "active_ff": s["ff"]}
+    m = TevilixForCausalLM(tc, tevilix_tensors(cfg, dev), device=dev, dtype=torch.bfloat16)
+    _throughput(m, s, timer, prompt, batch, ctx, out)
+    del m
+    torch.cuda.empty_cache()
+    mc = mutolix_config(s)   # the closest existing model: recurrent and attention layers in the same order, at the same sizes
+    mm = MutolixForCausalLM(MutolixConfig(mc), random_tensors(mc, dev), device=dev, dtype=torch.bfloat16)
+    _throughput(mm, s, timer, prompt, batch, ctx, out, prefix="mutolix_")
+    del mm
+    torch.cuda.empty_cache()
+    return out
+
+
+def tevilix_kernels(s: dict, dev, timer: Timer, prompt: int, ctx: int, hbm_gbs: float, tflops: float) -> dict:
+    """Every kernel of the design alone at this size, achieved / peak, beside the like kernel of the closest model."""
+    from . import _native_seq as nsq
+    bf, H, G, D, V, W, R, win = torch.bfloat16, s["H"], s["G"], s["D"], s["V"], s["width"], s["gru"], s["window"]
+    out = {}
+    gb = lambda by, ms: {"us": round(ms * 1e3, 2), "gb_s": round(by / ms / 1e6, 1), "of_measured_hbm_peak": round(by / ms / 1e6 / hbm_gbs, 4)}
+    tf = lambda fl, ms: {"ms": round(ms, 4), "tflops": round(fl / ms / 1e9, 1), "of_measured_bf16_peak": round(fl / ms / 1e9 / tflops, 3)}
+    cap = ((max(prompt, ctx + 1) + 127) // 128) * 128
+    b, b1 = nsq.Batch([0], [0], [prompt], dev), nsq.Batch([0], [ctx], [1], dev)
+    talk = torch.eye(H, device=dev) + torch.randn(H, H, device=dev) * 0.2
+    r1, r2 = torch.full((H,), 0.5, device=dev), torch.full((H,), 0.5, device=dev)
+    pairs = sum(min(i + 1, win) for i in range(prompt))       # visible (query, key) pairs of the prompt under the window
+    kp, vp = torch.randn(1, G, cap, D, device=dev).to(bf), torch.randn(1, G, cap, V, device=dev).to(bf)
+    q, o, og = torch.randn(prompt, H * D, device=dev).to(bf), torch.empty(prompt, H * V, device=dev, dtype=bf), torch.randn(prompt, H * V, device=dev).to(bf)
+    # prompt attention: FLOPs = 2 (D + V) per visible pair and head (the mixing's 2 H per pair and head comes on top and is not counted)
+    ms = timer(lambda: nsq.attention(q, kp, vp, o, H, D ** -0.5, None, None, False, b, window=win, talk=talk, out_gate=og))
+    out["attn_prompt_mixed_scores"] = dict(tf(2.0 * (D + V) * H * pairs, ms), uncounted_mixing_flops_share=round(H / (D + V), 3))
+    ms = timer(lambda: nsq.attention(q, kp, vp, o, H, D ** -0.5, r1, r2, True, b, window=win))
+    out["like_attn_prompt_same_window"] = tf(2.0 * (D + V) * H * pairs, ms)
+    ms = timer(lambda: nsq.attention(q, kp, vp, o, H, D ** -0.5, r1, r2, True, b))
+    out["like_attn_prompt_full_causal"] = tf(2.0 * (D + V) * H * prompt * (prompt + 1) / 2, ms)
+    # decoding: one token over its window; bytes = the window's K and V rows of all key/value heads once
+    q1, o1 = torch.randn(1, H * D, device=dev).to(bf), torch.empty(1, H * V, device=dev, dtype=bf)
+    ws = nsq.attn_workspace(1, H, V, dev)
+    seen = min(win, ctx + 1)
+    ms = timer(lambda: nsq.attention(q1, kp, vp, o1, H, D ** -0.5, None, None, False, b1, max_keys=seen, workspace=ws, window=win, talk=talk, out_gate=og[:1]), steps=15)
+    out["attn_decode_mixed_scores"] = gb(2.0 * G * seen * (D + V), ms)
+    ms = timer(lambda: nsq.attention(q1, kp, vp, o1, H, D ** -0.5, r1, r2, True, b1, max_keys=seen, workspace=ws, window=win), steps=15)
+    out["like_attn_decode_same_window"] = gb(2.0 * G * seen * (D + V), ms)
+    # head norms + rotation + append, beside Mutolix's whole-projection norms + append (both read the projection row, write q and K/V rows)
+    nq, nk = H * D, G * (D + V)
+    pj = torch.randn(prompt, nq + nk, device=dev).to(bf)
+    fr = torch.tensor([10000.0 ** (-2.0 * i / s["rot"]) / 4.0 for i in range(s["rot"] // 2)], dtype=torch.float64, device=dev)
+    hn = torch.ones(D, device=dev, dtype=bf)
+    ms = timer(lambda: nsq.rope_kv_prep(pj, (0, nq, nq + G * D), H, G, D, V, fr, s["rot"], False, False, 1e-5, q, kp, vp, b, q_norm_w=hn, k_norm_w=hn))
+    out["head_norm_rope_append"] = gb(prompt * (nq + nk) * 4.0, ms)
+    qn, kn = torch.ones(nq, device=dev, dtype=bf), torch.ones(G * D, device=dev, dtype=bf)
+    ms = timer(lambda: nsq.qk_prep(pj, (0, nq, nq + G * D), qn, kn, 1e-5, H, G, D, V, 0.0, 0, q, kp, vp, None, None, b))
+    out["like_qk_prep"] = gb(prompt * (nq + nk) * 4.0, ms)
+    # the layer's residual sum of three branch results with both norms of the next layer: reads x (4 B) and three results (2 + 2 + 4 B),
+    # writes x (4 B) and two inputs (2 + 2 B); like: gated norm + residual + next norm (reads y, gate, x; writes x, h)
+    x, wn = torch.randn(prompt, W, device=dev), torch.ones(W, device=dev, dtype=bf)
+    y1, y2, y3 = torch.randn(prompt, W, device=dev).to(bf), torch.randn(prompt, W, device=dev).to(bf), torch.randn(prompt, W, device=dev)
+    h1, h2 = torch.empty(prompt, W, device=dev, dtype=bf), torch.empty(prompt, W, device=dev, dtype=bf)
+    ms = timer(lambda: nsq.add_layer_norm(x, [(y1, 0.7), (y2, 0.8), (y3, 1.0)], 1e-5, wn, h1, wn, h2))
+    out["add3_two_layer_norms"] = gb(prompt * W * 20.0, ms)
+    ms = timer(lambda: nsq.gate_norm_add(x, y1, y2, wn, wn, 1e-5, wn, h1))
+    out["like_gate_norm_add"] = gb(prompt * W * 14.0, ms)
+    # the element-wise recurrence: reads three projections, writes the gated result (2 B each); one decoded token: state read and written
+    pr = torch.randn(prompt, 3 * R, device=dev).to(bf)
+    sp, go = torch.zeros(1, R, device=dev), torch.empty(prompt, R, device=dev, dtype=bf)
+    ms = timer(lambda: nsq.gru_scan(pr, (0, R, 2 * R), R, go, sp, b))
+    out["gru_scan_prompt"] = dict(gb(prompt * R * 8.0, ms), us_per_token=round(ms * 1e3 / prompt, 4))
+    ms = timer(lambda: nsq.gru_scan(pr[:1], (0, R, 2 * R), R, go[:1], sp, b1), steps=15)
+    out["gru_scan_decode"] = gb(R * 16.0, ms)
+    # the matrix memory is Mutolix's own kernel (same entry point, same sizes): listed for the step's budget
+    mH, mD, mV = s["mH"], s["mD"], s["mV"]
+    pm = (torch.randn(prompt, 2 * mH * mD + 2 * mH * mV, device=dev) * 0.3).to(bf)
+    offs = (0, mH * mD, 2 * mH * mD, 2 * mH * mD + mH * mV)
+    ig, fg = torch.randn(prompt, mH, device=dev), -torch.rand(prompt, mH, device=dev) * 0.1
+    spm, npool, mp = torch.zeros(1, mH, mD, mV, device=dev), torch.zeros(1, mH, mD, device=dev), torch.zeros(1, mH, device=dev)
+    nwm, om = torch.ones(mH * mV, device=dev, dtype=bf), torch.empty(prompt, mH * mV, device=dev, dtype=bf)
+    ms = timer(lambda: nsq.mlstm_scan(pm, offs, ig, fg, nwm, om, spm, npool, mp, 1e-5, b), steps=5)
+    out["shared_mlstm_scan_prompt"] = {"ms": round(ms, 3), "us_per_token": round(ms * 1e3 / prompt, 3), "gflops": round(4.0 * mH * mD * mV * prompt / ms / 1e6, 1)}
+    ms = timer(lambda: nsq.mlstm_scan(pm[:1], offs, ig[:1], fg[:1], nwm, om[:1], spm, npool, mp, 1e-5, b1), steps=15)
+    out["shared_mlstm_scan_decode"] = gb(8.0 * mH * mD * mV, ms)
+    # router, experts and the dense feed-forward's activation
+    E, top, ff = s["E"], s["top"], s["eff"]
+    hb = torch.randn(prompt, W, device=dev).to(bf)
+    wr, corr = (torch.randn(E, W, device=dev) * 3 * W ** -0.5).to(bf), torch.randn(E, device=dev) * 0.1
+    route = lambda: nsq.moe_route(hb, wr, corr, None, top, s["groups"][0], s["groups"][1], renorm=True, score_fn=nsq.ROUTE_SIGMOID, group_best=2, wgt_scale=2.0, renorm_eps=1e-20)
+    ms = timer(route)
+    out["moe_route_sigmoid_groups"] = gb(prompt * W * 2.0, ms)
+    idx, wgt, _ = route()
+    act = (nsq.ACT_RELU2, 0.0, 0.0)
+    wup, wdn = (torch.randn(E, ff, W, device=dev) * W ** -0.5).to(bf), (torch.randn(E, W, ff, device=dev) * ff ** -0.5).to(bf)
+    n_pairs = prompt * top
+    ms = timer(lambda: nsq.moe_experts(hb, idx, wup, wdn, grouped="library", act=act))
+    out["moe_experts_prompt"] = dict(tf(4.0 * ff * W * n_pairs, ms), what="plan + gather + library grouped products + squared relu")
+    xa = torch.randn(n_pairs, W, device=dev).to(bf)
+    ms = timer(lambda: torch.nn.functional.linear(torch.nn.functional.linear(xa, wup[0]), wdn[0]))
+    out["like_dense_ff_products"] = tf(4.0 * ff * W * n_pairs, ms)
+    i1 = idx[:1].contiguous()
+    ms = timer(lambda: nsq.moe_experts(hb[:1], i1, wup, wdn, grouped=False, act=act), steps=15)
+    out["moe_experts_decode"] = gb(top * 2.0 * ff * W * 2, ms)
+    wl = (torch.randn(top * 2 * ff, W, device=dev) * W ** -0.5).to(bf)
+    ms = timer(lambda: nsq.linear(hb[:1], wl, kernel=True), steps=15)
+    out["like_linear_rows"] = gb(top * 2.0 * ff * W * 2, ms)
+    u = torch.randn(prompt, s["ff"], device=dev).to(bf)
+    ms = timer(lambda: nsq.glu_mul(u, s["ff"], (nsq.ACT_GELU_ERF, 0.0, 0.0)))
+    out["gelu_erf"] = gb(prompt * s["ff"] * 4.0, ms)
+    ua, av = torch.empty_like(u), torch.randn(2, device=dev).to(bf)
+    ms = timer(lambda: nsq.xielu(u, ua, av))
+    out["like_xielu"] = gb(prompt * s["ff"] * 4.0, ms)
+    return out
+
+
+def run_tevilix(args, load_peaks, ClockSampler) -> None:
+    from . import _native_seq as nsq
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    nsq.load()
+    hbm, kind, tfl = load_peaks()
+    timer = Timer(dev)
+    sampler = ClockSampler(0)
+    sampler.start()
+    sampler.mark()
+    before = nsq.launch_count()
+    line = {"design": "tevilix", "compared_with": "mutolix (recurrent and attention layers in the same order, at the same sizes; where this design loops over "
+                                                  "four layers it has as many layers more) on the same step function, pool and kernels",
+            "dtype": "bf16", "data": "synthetic", "peaks": {"hbm_gbs": hbm, "bf16_tflops": tfl, "kind": kind},
+            "timing": "CUDA events, 3 warm-up iterations, 256 MiB L2 flush between iterations, median", "sizes": {}}
+    prompt, batch, ctx = 2048, 4, 2048
+    for name, s in TEVILIX_SIZES.items():
+        blk = tevilix_block(s, dev, timer, prompt, batch, ctx)
+        blk["kernels"] = tevilix_kernels(s, dev, timer, prompt, ctx, hbm, tfl)
+        line["sizes"][name] = blk
+    line["gpu_launches"] = nsq.launch_count() - before
+    line["clocks"] = sampler.stop()
+    print(json.dumps(line), flush=True)
+
+
 def run(args, load_peaks, ClockSampler) -> None:
+    if args.design == "tevilix":
+        return run_tevilix(args, load_peaks, ClockSampler)
     if args.design == "raritar":
         return run_raritar(args, load_peaks, ClockSampler)
     if args.design == "safilorn":
