@@ -7,11 +7,13 @@
 //             read in 16-byte pieces where the sizes allow;
 //   mix       (head, key) items again, H terms each, from the raw scores in shared memory;
 //   softmax   one warp per head, a key per lane: running maximum and sum in 32-bit, the tile's weights back to shared memory;
-//   values    (head, value column) items over the threads, each with its accumulator in a register.
+//   values    (head, value column) items over the threads, each with its accumulator in a register; the tile's value rows were
+//             asked for (L2 prefetch) before the scores, the next tile's key rows too.
 // The visible keys are a dense list (a sliding window plus kept first keys, or everything up to the query), so the work is
 // bounded by the window.  With several splits every block leaves (maximum, sum, accumulator) per head in the workspace, in the
 // layout the split merge of pcs_attn reads.  Both compute types; scores, weights and sums are 32-bit.
 #include "seq_common.cuh"
+#include "seq_mma.cuh"
 
 namespace pcs {
 
@@ -28,6 +30,18 @@ struct VisibleKeysT {   // the same dense list of visible keys as the other atte
   }
   __device__ __forceinline__ int key(int v) const { return v < n_first ? v : lo + (v - n_first); }
 };
+
+// asks L2 for `nt` rows (keys j0 ... of the visible list) of `width` elements of every key/value head, 128 bytes per request
+template <typename T>
+__device__ __forceinline__ void prefetch_rows(const T* base, long long head_stride, long long row_stride, int n_kv_heads, const VisibleKeysT& vis, int j0,
+                                              int nt, int width) {
+  constexpr int PER = 128 / static_cast<int>(sizeof(T));
+  const int lines = (width + PER - 1) / PER;
+  for (int e = threadIdx.x; e < n_kv_heads * nt * lines; e += TK_THREADS) {
+    const int line = e % lines, r = e / lines, jj = r % nt, g = r / nt;
+    prefetch_l2(base + g * head_stride + static_cast<long long>(vis.key(j0 + jj)) * row_stride + line * PER);
+  }
+}
 
 template <typename T>
 __global__ void __launch_bounds__(TK_THREADS) attn_talk_kernel(const pcs_attn_params p) {
@@ -56,10 +70,15 @@ __global__ void __launch_bounds__(TK_THREADS) attn_talk_kernel(const pcs_attn_pa
   float acc[TK_MAX_ACC];
 #pragma unroll
   for (int u = 0; u < TK_MAX_ACC; ++u) acc[u] = 0.f;
-  const bool vec = (D % Vec<T>::n) == 0 && (reinterpret_cast<uintptr_t>(K) & 15) == 0;
+  constexpr int N = Vec<T>::n;
+  const bool vec = (D % N) == 0 && (reinterpret_cast<uintptr_t>(K) & 15) == 0;
+  const bool vecv = (V % N) == 0 && (VS % N) == 0 && (reinterpret_cast<uintptr_t>(Vp) & 15) == 0;
   __syncthreads();
   for (int j0 = k_begin; j0 < k_end; j0 += TK_TILE) {
     const int nt = min(TK_TILE, k_end - j0);
+    // the tile's value rows, and the next tile's key rows, are on their way while the scores are formed
+    prefetch_rows(Vp, static_cast<long long>(p.cap) * VS, VS, G, vis, j0, nt, V);
+    if (j0 + TK_TILE < k_end) prefetch_rows(K, static_cast<long long>(p.cap) * D, D, G, vis, j0 + TK_TILE, min(TK_TILE, k_end - j0 - TK_TILE), D);
     // raw scores
     for (int e = tid; e < H * TK_TILE; e += TK_THREADS) {
       const int h = e / TK_TILE, jj = e - h * TK_TILE;
@@ -113,21 +132,46 @@ __global__ void __launch_bounds__(TK_THREADS) attn_talk_kernel(const pcs_attn_pa
       if (lane == 0) { mrun[h] = m_new; lrun[h] = lrun[h] * f + ts; fac[h] = f; }
     }
     __syncthreads();
-    // values
+    // values: a thread owns whole 16-byte pieces of a head's value row where the sizes allow (accumulator k of a thread belongs
+    // to the flat output column out_col(k)), else single columns
+    if (vecv) {
 #pragma unroll
-    for (int u = 0; u < TK_MAX_ACC; ++u) {
-      const int e = tid + u * TK_THREADS;
-      if (e < H * V) {
-        const int h = e / V, c = e - h * V;
-        const T* vr = Vp + static_cast<long long>(h / rep) * p.cap * VS + c;
-        const float* wh = sw + h * TK_TILE;
-        float a = acc[u] * fac[h];
-        for (int jj = 0; jj < nt; ++jj) a = fmaf(wh[jj], ldf(vr + static_cast<long long>(vis.key(j0 + jj)) * VS), a);
-        acc[u] = a;
+      for (int u = 0; u < TK_MAX_ACC / N; ++u) {
+        const int e = tid + u * TK_THREADS;
+        if (e < H * V / N) {
+          const int h = e / (V / N), c = (e - h * (V / N)) * N;
+          const T* vr = Vp + static_cast<long long>(h / rep) * p.cap * VS + c;
+          const float* wh = sw + h * TK_TILE;
+          const float f = fac[h];
+#pragma unroll
+          for (int i = 0; i < N; ++i) acc[u * N + i] *= f;
+          for (int jj = 0; jj < nt; ++jj) {
+            float vv[N];
+            ld16(vr + static_cast<long long>(vis.key(j0 + jj)) * VS, vv);
+            const float w = wh[jj];
+#pragma unroll
+            for (int i = 0; i < N; ++i) acc[u * N + i] = fmaf(w, vv[i], acc[u * N + i]);
+          }
+        }
+      }
+    } else {
+#pragma unroll
+      for (int u = 0; u < TK_MAX_ACC; ++u) {
+        const int e = tid + u * TK_THREADS;
+        if (e < H * V) {
+          const int h = e / V, c = e - h * V;
+          const T* vr = Vp + static_cast<long long>(h / rep) * p.cap * VS + c;
+          const float* wh = sw + h * TK_TILE;
+          float a = acc[u] * fac[h];
+          for (int jj = 0; jj < nt; ++jj) a = fmaf(wh[jj], ldf(vr + static_cast<long long>(vis.key(j0 + jj)) * VS), a);
+          acc[u] = a;
+        }
       }
     }
     __syncthreads();
   }
+  // accumulator k of this thread -> flat output column
+  auto out_col = [&](int k) { return vecv ? (tid + (k / N) * TK_THREADS) * N + (k % N) : tid + k * TK_THREADS; };
   if (S > 1) {
     if (tid < H) {
       float* part = p.workspace + ((static_cast<long long>(t) * H + tid) * S + sp) * (V + 2);
@@ -136,7 +180,7 @@ __global__ void __launch_bounds__(TK_THREADS) attn_talk_kernel(const pcs_attn_pa
     }
 #pragma unroll
     for (int u = 0; u < TK_MAX_ACC; ++u) {
-      const int e = tid + u * TK_THREADS;
+      const int e = out_col(u);
       if (e < H * V) {
         const int h = e / V, c = e - h * V;
         p.workspace[((static_cast<long long>(t) * H + h) * S + sp) * (V + 2) + 2 + c] = acc[u];
@@ -147,7 +191,7 @@ __global__ void __launch_bounds__(TK_THREADS) attn_talk_kernel(const pcs_attn_pa
   T* o = static_cast<T*>(p.out) + static_cast<long long>(t) * H * V;
 #pragma unroll
   for (int u = 0; u < TK_MAX_ACC; ++u) {
-    const int e = tid + u * TK_THREADS;
+    const int e = out_col(u);
     if (e < H * V) {
       const float l = lrun[e / V];
       float a = l > 0.f ? acc[u] / l : 0.f;
@@ -176,9 +220,9 @@ int launch_attn_talk(const pcs_attn_params& p, cudaStream_t st, int* splits_out)
   const size_t smem = (static_cast<size_t>(H) * p.dim + static_cast<size_t>(H) * H + 2 * static_cast<size_t>(H) * TK_TILE + 3 * static_cast<size_t>(H)) * sizeof(float);
   PCS_REQUIRE(smem <= 200 * 1024, "pcs_attn: mixed head scores: %zu bytes of shared memory per token exceed the limit", smem);
   int splits = 1;
-  if (p.workspace != nullptr && p.max_keys > 4 * TK_TILE) {   // few tokens: the keys are split so that the launch fills more of the GPU
+  if (p.workspace != nullptr && p.max_keys > 2 * TK_TILE) {   // few tokens: the keys are split so that the launch fills more of the GPU
     const int want = (2 * 148 + p.n_tokens - 1) / p.n_tokens;
-    splits = p.max_keys / (2 * TK_TILE);
+    splits = p.max_keys / TK_TILE;   // down to one tile per block: the tiles of a block run one after the other
     if (splits > want) splits = want;
     if (splits > 64) splits = 64;
     if (splits < 1) splits = 1;

@@ -7,8 +7,8 @@
 //     S_g = scale * Q_g K^T   m16n8k16 bfloat16 products of the warp's own heads (query rows of all heads sit in shared memory;
 //                             an A fragment is loaded once per 16 coordinates and meets all key columns of the tile), the 32-bit
 //                             raw scores of ALL heads go to shared memory
-//     mix                     every thread reads, for the score positions of its accumulator fragment, the H raw scores and forms
-//                             its own heads' mixed scores in 32-bit; then the causal / window mask
+//     mix                     every thread reads, for the score positions of its accumulator fragment, the H raw scores (once for
+//                             all heads of its warp) and forms its own heads' mixed scores in 32-bit; then the causal / window mask
 //     online softmax          running maximum / sum per query row and head in 32-bit
 //     O_h += P_h V            the 32-bit weights enter the tensor cores as TWO bfloat16 operands (hi + lo), V through ldmatrix.trans
 // and at the end O / l, times the element-wise sigmoid gate when one is given.  Head widths are padded in shared memory to 64
@@ -20,18 +20,18 @@ namespace pcs {
 
 namespace {
 
-constexpr int TT_THREADS = 256, TT_WARPS = 8, TT_BM = 16, TT_PAD = 8;
+constexpr int TT_BM = 16, TT_PAD = 8;
 
 __device__ __forceinline__ uint32_t lds32(const __nv_bfloat16* p) { return *reinterpret_cast<const uint32_t*>(p); }
 
 // rows [row0, row0 + n_rows_tile) x `width` of `heads` matrices (head hd at src + hd * head_stride, rows `row_stride` apart) into
 // dst[(hd * n_rows_tile + r)][WP + PAD]; rows >= n_rows and columns >= width are zero
-template <int WP>
+template <int WP, int THREADS>
 __device__ __forceinline__ void load_rows_async(__nv_bfloat16* dst, const __nv_bfloat16* src, long long head_stride, long long row_stride, int heads,
                                                 int n_rows_tile, int row0, int n_rows, int width) {
   constexpr int CH = WP / 8;
   const int total = heads * n_rows_tile * CH;
-  for (int e = threadIdx.x; e < total; e += TT_THREADS) {
+  for (int e = threadIdx.x; e < total; e += THREADS) {
     const int c = (e % CH) * 8, hr = e / CH, r = hr % n_rows_tile, hd = hr / n_rows_tile;
     __nv_bfloat16* d = dst + static_cast<long long>(hr) * (WP + TT_PAD) + c;
     if (row0 + r < n_rows && c < width) cp_async16(d, src + hd * head_stride + static_cast<long long>(row0 + r) * row_stride + c);
@@ -39,9 +39,9 @@ __device__ __forceinline__ void load_rows_async(__nv_bfloat16* dst, const __nv_b
   }
 }
 
-template <int WP, int HPW, int BN>
-__global__ void __launch_bounds__(TT_THREADS, 1) attn_talk_tc_kernel(const pcs_attn_params p) {
-  constexpr int LD = WP + TT_PAD, NT = BN / 8, LDS_S = BN + 8;
+template <int WP, int HPW, int BN, int NW, int MINB>
+__global__ void __launch_bounds__(NW * 32, MINB) attn_talk_tc_kernel(const pcs_attn_params p) {
+  constexpr int LD = WP + TT_PAD, NT = BN / 8, LDS_S = BN + 8, TT_THREADS = NW * 32;
   extern __shared__ __align__(16) unsigned char smem_raw[];
   const int H = p.n_heads, G = p.n_kv_heads, D = p.dim, V = p.vdim, rep = H / G;
   __nv_bfloat16* Qs = reinterpret_cast<__nv_bfloat16*>(smem_raw);            // [H][16][LD]
@@ -64,10 +64,10 @@ __global__ void __launch_bounds__(TT_THREADS, 1) attn_talk_tc_kernel(const pcs_a
   const long long VS = p.v_row_stride > 0 ? p.v_row_stride : V;
   const __nv_bfloat16* Vg = static_cast<const __nv_bfloat16*>(p.v_pool) + static_cast<long long>(slot) * G * p.cap * VS;
   // queries of all heads: head hd's rows are H * D apart
-  load_rows_async<WP>(Qs, Q, D, static_cast<long long>(H) * D, H, TT_BM, 0, rows, D);
-  load_rows_async<WP>(Ks, K, static_cast<long long>(p.cap) * D, D, G, BN, lo, n_ctx, D);
+  load_rows_async<WP, TT_THREADS>(Qs, Q, D, static_cast<long long>(H) * D, H, TT_BM, 0, rows, D);
+  load_rows_async<WP, TT_THREADS>(Ks, K, static_cast<long long>(p.cap) * D, D, G, BN, lo, n_ctx, D);
   cp_async_commit();
-  load_rows_async<WP>(Vs, Vg, static_cast<long long>(p.cap) * VS, VS, G, BN, lo, n_ctx, V);
+  load_rows_async<WP, TT_THREADS>(Vs, Vg, static_cast<long long>(p.cap) * VS, VS, G, BN, lo, n_ctx, V);
   cp_async_commit();
   for (int i = tid; i < H * H; i += TT_THREADS) Tk[i] = p.talk[i];
   float oacc[HPW][WP / 8][4];
@@ -114,30 +114,37 @@ __global__ void __launch_bounds__(TT_THREADS, 1) attn_talk_tc_kernel(const pcs_a
     }
     cp_async_wait<0>();      // V of this tile
     __syncthreads();         // all heads' raw scores are there; K's buffer is free
-    if (jt + 1 < n_tiles) load_rows_async<WP>(Ks, K, static_cast<long long>(p.cap) * D, D, G, BN, j0 + BN, n_ctx, D);
+    if (jt + 1 < n_tiles) load_rows_async<WP, TT_THREADS>(Ks, K, static_cast<long long>(p.cap) * D, D, G, BN, j0 + BN, n_ctx, D);
     cp_async_commit();
-    // ---- own heads: mix, mask, softmax, P V
+    // ---- own heads: mix (every raw score is read once for all heads of the warp), mask, softmax, P V
+    float sm_[HPW][NT][4];
+#pragma unroll
+    for (int i = 0; i < HPW; ++i)
+#pragma unroll
+      for (int n = 0; n < NT; ++n) sm_[i][n][0] = sm_[i][n][1] = sm_[i][n][2] = sm_[i][n][3] = 0.f;
+    for (int g2 = 0; g2 < H; ++g2) {
+      float w[HPW];
+#pragma unroll
+      for (int i = 0; i < HPW; ++i) w[i] = warp * HPW + i < H ? Tk[(warp * HPW + i) * H + g2] : 0.f;
+      const float* sg = Ss + static_cast<long long>(g2) * TT_BM * LDS_S;
+#pragma unroll
+      for (int n = 0; n < NT; ++n) {
+        const float2 u = *reinterpret_cast<const float2*>(sg + gq * LDS_S + n * 8 + 2 * tq);
+        const float2 v = *reinterpret_cast<const float2*>(sg + (gq + 8) * LDS_S + n * 8 + 2 * tq);
+#pragma unroll
+        for (int i = 0; i < HPW; ++i) {
+          sm_[i][n][0] = fmaf(w[i], u.x, sm_[i][n][0]);
+          sm_[i][n][1] = fmaf(w[i], u.y, sm_[i][n][1]);
+          sm_[i][n][2] = fmaf(w[i], v.x, sm_[i][n][2]);
+          sm_[i][n][3] = fmaf(w[i], v.y, sm_[i][n][3]);
+        }
+      }
+    }
 #pragma unroll
     for (int i = 0; i < HPW; ++i) {
       const int h = warp * HPW + i;
       if (h < H) {
-        float s[NT][4];
-#pragma unroll
-        for (int n = 0; n < NT; ++n) s[n][0] = s[n][1] = s[n][2] = s[n][3] = 0.f;
-        const float* tr = Tk + h * H;
-        for (int g2 = 0; g2 < H; ++g2) {
-          const float w = tr[g2];
-          const float* sg = Ss + static_cast<long long>(g2) * TT_BM * LDS_S;
-#pragma unroll
-          for (int n = 0; n < NT; ++n) {
-            const float2 u = *reinterpret_cast<const float2*>(sg + gq * LDS_S + n * 8 + 2 * tq);
-            const float2 v = *reinterpret_cast<const float2*>(sg + (gq + 8) * LDS_S + n * 8 + 2 * tq);
-            s[n][0] = fmaf(w, u.x, s[n][0]);
-            s[n][1] = fmaf(w, u.y, s[n][1]);
-            s[n][2] = fmaf(w, v.x, s[n][2]);
-            s[n][3] = fmaf(w, v.y, s[n][3]);
-          }
-        }
+        float (&s)[NT][4] = sm_[i];
         float mx_a = -INFINITY, mx_b = -INFINITY;
 #pragma unroll
         for (int n = 0; n < NT; ++n) {
@@ -205,7 +212,7 @@ __global__ void __launch_bounds__(TT_THREADS, 1) attn_talk_tc_kernel(const pcs_a
       }
     }
     __syncthreads();         // V's buffer and the raw scores are free
-    if (jt + 1 < n_tiles) load_rows_async<WP>(Vs, Vg, static_cast<long long>(p.cap) * VS, VS, G, BN, j0 + BN, n_ctx, V);
+    if (jt + 1 < n_tiles) load_rows_async<WP, TT_THREADS>(Vs, Vg, static_cast<long long>(p.cap) * VS, VS, G, BN, j0 + BN, n_ctx, V);
     cp_async_commit();
   }
   cp_async_wait<0>();
@@ -241,15 +248,15 @@ __global__ void __launch_bounds__(TT_THREADS, 1) attn_talk_tc_kernel(const pcs_a
   }
 }
 
-template <int WP, int HPW, int BN>
+template <int WP, int HPW, int BN, int NW, int MINB>
 int launch_one(const pcs_attn_params& p, cudaStream_t st, size_t smem) {
   static bool configured = false;
   if (!configured) {
-    PCS_CHECK_CUDA(cudaFuncSetAttribute(attn_talk_tc_kernel<WP, HPW, BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, 220 * 1024));
+    PCS_CHECK_CUDA(cudaFuncSetAttribute(attn_talk_tc_kernel<WP, HPW, BN, NW, MINB>, cudaFuncAttributeMaxDynamicSharedMemorySize, 220 * 1024));
     configured = true;
   }
   const int n_qtiles = (p.max_len + TT_BM - 1) / TT_BM;
-  attn_talk_tc_kernel<WP, HPW, BN><<<p.n_seqs * n_qtiles, TT_THREADS, smem, st>>>(p);
+  attn_talk_tc_kernel<WP, HPW, BN, NW, MINB><<<p.n_seqs * n_qtiles, NW * 32, smem, st>>>(p);
   PCS_CHECK_CUDA(cudaGetLastError());
   count_launch();
   return PCS_OK;
@@ -271,14 +278,16 @@ int launch_attn_talk_tc(const pcs_attn_params& p, cudaStream_t st, bool* handled
                     (p.v_row_stride == 0 || p.v_row_stride % 8 == 0) &&
                     (p.out_gate == nullptr || ((reinterpret_cast<uintptr_t>(p.out_gate) & 3) == 0 && p.out_gate_stride % 2 == 0));
   if (!fits) return PCS_OK;
-  const int WP = wmax <= 64 ? 64 : 128, HPW = p.n_heads <= TT_WARPS ? 1 : 2;
+  // 8 warps; up to 8 heads one head per warp, up to 16 two; tiles of 64 keys where the shared memory allows, else 32.  (Measured
+  // alternatives that were slower at 8 / 16 heads of 128: two blocks per SM at 128 registers, 16 warps with one head each.)
+  const int WP = wmax <= 64 ? 64 : 128, HPW = p.n_heads <= 8 ? 1 : 2;
   const size_t limit = 220 * 1024;
   int BN = 64;
   if (talk_tc_smem(p.n_heads, p.n_kv_heads, WP, 64) > limit) BN = 32;
   const size_t smem = talk_tc_smem(p.n_heads, p.n_kv_heads, WP, BN);
   if (smem > limit) return PCS_OK;
   *handled = true;
-#define PCS_TT(W_, H_, B_) if (WP == W_ && HPW == H_ && BN == B_) return launch_one<W_, H_, B_>(p, st, smem)
+#define PCS_TT(W_, H_, B_) if (WP == W_ && HPW == H_ && BN == B_) return launch_one<W_, H_, B_, 8, 1>(p, st, smem)
   PCS_TT(64, 1, 64); PCS_TT(64, 2, 64); PCS_TT(128, 1, 64); PCS_TT(128, 2, 64);
   PCS_TT(64, 1, 32); PCS_TT(64, 2, 32); PCS_TT(128, 1, 32); PCS_TT(128, 2, 32);
 #undef PCS_TT
