@@ -21,8 +21,8 @@
  *                        time whose last inputs are carried in the slot pool
  *   pcs_rope_kv_prep     rotation of a leading part of every query / key head by position (arbitrary frequency table),
  *                        unit-RMS values, append of K/V rows to the slot pool
- *   pcs_moe_route        router of a mixture of experts: softmax scores, choice with a correction and group limits
- *   pcs_moe_rows_*       the chosen experts' gated feed-forward for a handful of rows (weights streamed once)
+ *   pcs_moe_route        router of a mixture of experts: softmax or sigmoid scores, choice with a correction and group limits
+ *   pcs_moe_rows_*       the chosen experts' feed-forward (gated, or one up-projection) for a handful of rows (weights streamed once)
  *   pcs_moe_plan/_gemm   the same for many rows: rows sorted by expert, grouped tensor-core products
  *   pcs_moe_combine      weighted sum of expert results, pass-through experts and a gated shared expert into the residual
  *   pcs_silu_mul         silu(gate) * up;  pcs_glu_mul: the same with the activation as a parameter
@@ -256,8 +256,9 @@ typedef struct pcs_rope_params {
 } pcs_rope_params;
 int pcs_rope_kv_prep(const pcs_rope_params* p, void* stream);
 
-/* Router of a mixture of experts, per token: z = w_router h (32-bit sums), s = softmax(z) over all n_outputs, choice scores
- * c = s + correction.  Outputs form n_groups equal groups of neighbours; a group's score is its largest c; only outputs of
+/* Router of a mixture of experts, per token: z = w_router h (32-bit sums), s = softmax(z) over all n_outputs (or sigmoid(z), see
+ * score_fn), choice scores c = s + correction.  Outputs form n_groups equal groups of neighbours; a group's score is its largest c
+ * (or the sum of its group_best largest); only outputs of
  * the keep_groups best groups can be chosen; the `top` largest c among them are chosen (ties: the lower index).
  * idx[t, k] = the k-th choice, wgt[t, k] = s of it (not renormalised).  shared_gate[t] = sigmoid(w_sg . h) when w_sg is given. */
 typedef struct pcs_route_params {
@@ -297,7 +298,8 @@ typedef struct pcs_glu_act {
 /* The chosen experts for a handful of rows.  Pair p = (token p / top, choice p % top), expert e = idx[p]; e >= n_experts is a
  * pass-through output and is skipped.  w_gu [n_experts, 2*ff, width] (gate rows, then up rows), w_down [n_experts, width, ff].
  *   pcs_moe_rows_up:    act[p, :] = silu(W_gate_e h) * (W_up_e h)        act `dtype` [pairs, ff]
- *   pcs_moe_rows_down:  y[p, :]  = W_down_e act[p, :]                    y fp32 [pairs, width] */
+ *   pcs_moe_rows_down:  y[p, :]  = W_down_e act[p, :]                    y fp32 [pairs, width]
+ * With an activation that has no gate branch (PCS_ACT_*) w_gu is [n_experts, ff, width] and act[p, :] = act(W_up_e h). */
 int pcs_moe_rows_up(const void* h, int64_t h_stride, const void* w_gu, const int32_t* idx, void* act, int n_pairs, int top, int n_experts,
                     int ff, int width, const pcs_glu_act* glu, int dtype, void* stream);
 int pcs_moe_rows_down(const void* act, const void* w_down, const int32_t* idx, float* y, int n_pairs, int n_experts, int ff, int width,
