@@ -19,7 +19,7 @@ namespace pcs {
 
 namespace {
 
-constexpr int TK_THREADS = 256, TK_TILE = 32, TK_MAX_ACC = 16;
+constexpr int TK_THREADS = 256, TK_TILE = 32, TK_MAX_ACC = 32;   // heads x vdim <= 8192
 
 struct VisibleKeysT {   // the same dense list of visible keys as the other attention kernels use
   int n_first, lo, count;

@@ -8,7 +8,8 @@
 //                             an A fragment is loaded once per 16 coordinates and meets all key columns of the tile), the 32-bit
 //                             raw scores of ALL heads go to shared memory
 //     mix                     every thread reads, for the score positions of its accumulator fragment, the H raw scores (once for
-//                             all heads of its warp) and forms its own heads' mixed scores in 32-bit; then the causal / window mask
+//                             all heads of its warp) and forms its own heads' mixed scores in 32-bit, two multiply-adds per
+//                             instruction; then the causal / window mask
 //     online softmax          running maximum / sum per query row and head in 32-bit
 //     O_h += P_h V            the 32-bit weights enter the tensor cores as TWO bfloat16 operands (hi + lo), V through ldmatrix.trans
 // and at the end O / l, times the element-wise sigmoid gate when one is given.  Head widths are padded in shared memory to 64
@@ -132,11 +133,14 @@ __global__ void __launch_bounds__(NW * 32, MINB) attn_talk_tc_kernel(const pcs_a
         const float2 u = *reinterpret_cast<const float2*>(sg + gq * LDS_S + n * 8 + 2 * tq);
         const float2 v = *reinterpret_cast<const float2*>(sg + (gq + 8) * LDS_S + n * 8 + 2 * tq);
 #pragma unroll
-        for (int i = 0; i < HPW; ++i) {
-          sm_[i][n][0] = fmaf(w[i], u.x, sm_[i][n][0]);
-          sm_[i][n][1] = fmaf(w[i], u.y, sm_[i][n][1]);
-          sm_[i][n][2] = fmaf(w[i], v.x, sm_[i][n][2]);
-          sm_[i][n][3] = fmaf(w[i], v.y, sm_[i][n][3]);
+        for (int i = 0; i < HPW; ++i) {   // two 32-bit multiply-adds per instruction (fma.rn.f32x2)
+          const float2 ww = make_float2(w[i], w[i]);
+          const float2 a = __ffma2_rn(ww, u, make_float2(sm_[i][n][0], sm_[i][n][1]));
+          const float2 c = __ffma2_rn(ww, v, make_float2(sm_[i][n][2], sm_[i][n][3]));
+          sm_[i][n][0] = a.x;
+          sm_[i][n][1] = a.y;
+          sm_[i][n][2] = c.x;
+          sm_[i][n][3] = c.y;
         }
       }
     }
@@ -279,7 +283,8 @@ int launch_attn_talk_tc(const pcs_attn_params& p, cudaStream_t st, bool* handled
                     (p.out_gate == nullptr || ((reinterpret_cast<uintptr_t>(p.out_gate) & 3) == 0 && p.out_gate_stride % 2 == 0));
   if (!fits) return PCS_OK;
   // 8 warps; up to 8 heads one head per warp, up to 16 two; tiles of 64 keys where the shared memory allows, else 32.  (Measured
-  // alternatives that were slower at 8 / 16 heads of 128: two blocks per SM at 128 registers, 16 warps with one head each.)
+  // alternatives that were not faster at 8 / 16 heads of 128, also with thousands of blocks: two blocks per SM at 128 registers and
+  // 32-key tiles, 16 warps with one head each.)
   const int WP = wmax <= 64 ? 64 : 128, HPW = p.n_heads <= 8 ? 1 : 2;
   const size_t limit = 220 * 1024;
   int BN = 64;

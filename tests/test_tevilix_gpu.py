@@ -163,7 +163,9 @@ def _attention_case(nsq, dtype, H, G, D, V, N, T, window, talk, impl=0, gate=Tru
 
 @pytest.mark.parametrize("dtype,H,G,D,V,N,T,window", [(F32, 4, 2, 12, 10, 70, 70, 9), (F32, 3, 1, 7, 5, 45, 3, 0), (F32, 5, 5, 8, 8, 700, 1, 0), (BF16, 8, 2, 32, 16, 300, 300, 45),
                                                        (BF16, 4, 4, 64, 64, 700, 2, 256), (F32, 2, 2, 16, 8, 33, 33, 1), (F32, 6, 3, 24, 20, 900, 4, 600),
-                                                       (BF16, 8, 4, 96, 64, 520, 520, 52), (BF16, 16, 4, 64, 64, 400, 400, 128), (BF16, 4, 1, 128, 128, 333, 333, 0)])
+                                                       (BF16, 8, 4, 96, 64, 520, 520, 52), (BF16, 16, 4, 64, 64, 400, 400, 128), (BF16, 4, 1, 128, 128, 333, 333, 0),
+                                                       (BF16, 12, 3, 48, 80, 200, 200, 33), (BF16, 6, 2, 128, 64, 150, 150, 0), (BF16, 9, 9, 24, 8, 90, 90, 17),
+                                                       (F32, 40, 8, 16, 160, 70, 5, 20)])
 def test_attention_with_scores_mixed_across_heads(nsq, dtype, H, G, D, V, N, T, window):
     g = torch.Generator().manual_seed(H)
     talk = (torch.eye(H, dtype=F64) + 0.4 * torch.randn(H, H, generator=g, dtype=F64)).to(F32).to(F64)
@@ -172,6 +174,33 @@ def test_attention_with_scores_mixed_across_heads(nsq, dtype, H, G, D, V, N, T, 
         close(out, want, 2e-5 if dtype == F32 else 2e-2, f"mixed scores, window {window}, impl {impl}")
     out, want = _attention_case(nsq, dtype, H, G, D, V, N, T, window, talk, gate=False)
     close(out, want, 2e-5 if dtype == F32 else 2e-2, "without the output gate")
+
+
+@pytest.mark.parametrize("dtype,H,G,D,V,window", [(BF16, 8, 2, 64, 64, 48), (BF16, 12, 4, 32, 48, 0), (F32, 4, 2, 16, 8, 20), (BF16, 16, 16, 32, 32, 200)])
+def test_mixed_score_attention_in_portions_and_unequal_batches(nsq, dtype, H, G, D, V, window):
+    """Entries that continue a sequence (their slots already hold rows) beside one that starts, of unequal lengths, in shuffled slots:
+    every kernel that serves the shape must see each entry's own rows at its own positions, and nothing of the other slots."""
+    g = torch.Generator().manual_seed(H * 7 + D)
+    talk = (torch.eye(H, dtype=F64) + 0.3 * torch.randn(H, H, generator=g, dtype=F64)).to(F32).to(F64)
+    pos0, lens, slots, cap = [0, 37, 300, 129], [50, 16, 90, 1], [3, 0, 2, 5], 512
+    B, T = len(lens), sum(lens)
+    ks = [torch.randn(p + n, G, D, generator=g, dtype=F64).to(dtype).to(F64) for p, n in zip(pos0, lens)]
+    vs = [torch.randn(p + n, G, V, generator=g, dtype=F64).to(dtype).to(F64) for p, n in zip(pos0, lens)]
+    q = torch.randn(T, H, D, generator=g, dtype=F64).to(dtype).to(F64)
+    kp = torch.randn(6, G, cap, D, generator=g).to(DEV, dtype) * 3       # other slots and later rows hold numbers that must not show
+    vp = torch.randn(6, G, cap, V, generator=g).to(DEV, dtype) * 3
+    for s_, k_, v_ in zip(slots, ks, vs):
+        kp[s_, :, :k_.shape[0]], vp[s_, :, :v_.shape[0]] = dev(k_, dtype).transpose(0, 1), dev(v_, dtype).transpose(0, 1)
+    b = batch_of(nsq, slots, pos0, lens)
+    want, o = [], 0
+    for p, n, k_, v_ in zip(pos0, lens, ks, vs):
+        want.append(O.mixed_score_attention(q[o:o + n], k_, v_, torch.arange(p, p + n), torch.arange(p + n), 0.25, talk, window).reshape(n, H * V))
+        o += n
+    want = torch.cat(want)
+    for impl in ((0, 1) if dtype == BF16 else (0,)):
+        out = torch.empty(T, H * V, device=DEV, dtype=dtype)
+        nsq.attention(dev(q.reshape(T, H * D), dtype), kp, vp, out, H, 0.25, None, None, False, b, impl=impl, window=window, talk=dev(talk))
+        close(out, want, 2e-5 if dtype == F32 else 2e-2, f"portions and unequal entries, impl {impl}")
 
 
 @pytest.mark.parametrize("dtype,T", [(F32, 1), (F32, 80), (BF16, 1), (BF16, 80)])
@@ -410,6 +439,40 @@ def test_portions_decoding_batches_and_slot_reuse(tmp_path, dtype, tol):
         close(lg, ref, tol, "reused slots")
     else:
         close_rows(lg, ref, 0.3, "reused slots", share=0.6)   # three rows at the sequences' ends, where bfloat16 noise of tiny heads has piled up
+
+
+@pytest.mark.parametrize("dtype,tol", [(F32, 5e-5), (BF16, 6e-2)])
+def test_tensor_core_sizes_in_portions_and_batches(tmp_path, dtype, tol):
+    """Head sizes that the tensor-core kernels serve (multiples of 8), prompts cut into portions of 16 tokens and more that continue
+    a sequence, and an unequal batch of prompts: the portions' windows (24 and 70 tokens) reach back into rows of earlier steps."""
+    P, M = O.parallel_layer, O.mlstm_layer
+    cfg = O.make_config([P(heads=8, kv_heads=2, dim=32, vdim=32, window=24, rot_dims=16, gru=40, mlp=O.moe(experts=4, top=2, ff=32, groups=2, keep=1)),
+                         M(heads=2, dim=32, vdim=32), P(heads=4, kv_heads=4, dim=64, vdim=16, window=70, rot_dims=64, gru=24)], width=64, loop=(1, 3, 2))
+    W = O.random_model(cfg, seed=17)
+    seqs = [tokens(n, cfg["vocab"], 70 + n) for n in (150, 33, 80)]
+    want = [O.forward(cfg, W, s) for s in seqs]
+    m = load(tmp_path, cfg, W, dtype)
+    cmp = close if dtype == F32 else (lambda g_, w_, t_, s_: close_rows(g_, w_, t_, s_, share=0.7))
+    for cuts in ([150], [40, 17, 64, 29], [16, 16, 100, 2, 16], [149, 1]):
+        seq, out, p_ = m.new_sequence(), [], 0
+        for n in cuts:
+            out.append(m.step([(seq, seqs[0][p_:p_ + n])], [list(range(n))]))
+            p_ += n
+        seq.free()
+        cmp(torch.cat(out), want[0], tol, f"portions {cuts}")
+    # three prompts of unequal length as one batch, cut in two steps at different places
+    ss = [m.new_sequence() for _ in seqs]
+    first = [70, 17, 40]
+    a = m.step([(q_, s_[:n]) for q_, s_, n in zip(ss, seqs, first)], [list(range(n)) for n in first])
+    b = m.step([(q_, s_[n:]) for q_, s_, n in zip(ss, seqs, first)], [list(range(len(s_) - n)) for s_, n in zip(seqs, first)])
+    oa = ob = 0
+    for i, (s_, n) in enumerate(zip(seqs, first)):
+        got = torch.cat([a[oa:oa + n], b[ob:ob + len(s_) - n]])
+        cmp(got, want[i], tol, f"request {i} of the batch")
+        oa += n
+        ob += len(s_) - n
+    for q_ in ss:
+        q_.free()
 
 
 def test_long_decoding_window_passes_over_decoded_tokens(tmp_path):
