@@ -49,7 +49,7 @@ __global__ void __launch_bounds__(NW * 32, MINB) attn_talk_tc_kernel(const pcs_a
   __nv_bfloat16* Ks = Qs + H * TT_BM * LD;                                    // [G][BN][LD]
   __nv_bfloat16* Vs = Ks + G * BN * LD;                                       // [G][BN][LD]
   float* Ss = reinterpret_cast<float*>(Vs + G * BN * LD);                     // [H][16][BN + 8] raw scores
-  float* Tk = Ss + H * TT_BM * LDS_S;                                         // [H][H]
+  float* Tk = Ss + H * TT_BM * LDS_S;                                         // [warps * HPW][H]
   const int n_qtiles = (p.max_len + TT_BM - 1) / TT_BM;
   const int b = blockIdx.x / n_qtiles, qt = n_qtiles - 1 - blockIdx.x % n_qtiles;   // long tiles first
   const int len = p.seq_len[b], q0 = qt * TT_BM;
@@ -70,7 +70,6 @@ __global__ void __launch_bounds__(NW * 32, MINB) attn_talk_tc_kernel(const pcs_a
   cp_async_commit();
   load_rows_async<WP, TT_THREADS>(Vs, Vg, static_cast<long long>(p.cap) * VS, VS, G, BN, lo, n_ctx, V);
   cp_async_commit();
-  for (int i = tid; i < H * H; i += TT_THREADS) Tk[i] = p.talk[i];
   float oacc[HPW][WP / 8][4];
   float mrow[HPW][2], lrow[HPW][2];
 #pragma unroll
@@ -81,8 +80,14 @@ __global__ void __launch_bounds__(NW * 32, MINB) attn_talk_tc_kernel(const pcs_a
     for (int n = 0; n < WP / 8; ++n) oacc[i][n][0] = oacc[i][n][1] = oacc[i][n][2] = oacc[i][n][3] = 0.f;
   }
   const int pos_a = qp0 + gq, pos_b = qp0 + gq + 8;      // positions of the thread's two query rows
+  // the rows of the mixing matrix of this warp's heads (zero for heads past H); the score scale rides in them
+  float* Tw = Tk + warp * HPW * H;
+  for (int e = lane; e < HPW * H; e += 32) Tw[e] = warp * HPW + e / H < H ? p.talk[(warp * HPW + e / H) * H + e % H] * p.scale : 0.f;
+  __syncwarp();
   for (int jt = 0; jt < n_tiles; ++jt) {
     const int j0 = lo + jt * BN;
+    // all keys of the tile at or before the first query and inside the last valid row's window: nothing to mask
+    const bool full_tile = j0 + BN - 1 <= qp0 && (p.window <= 0 || (qp0 + TT_BM - 1) - j0 < p.window);
     cp_async_wait<1>();      // K of this tile (and, on the first tile, Q)
     __syncthreads();
     // ---- raw scores of the warp's own heads -> shared memory
@@ -108,8 +113,8 @@ __global__ void __launch_bounds__(NW * 32, MINB) attn_talk_tc_kernel(const pcs_a
         float* sh = Ss + static_cast<long long>(h) * TT_BM * LDS_S;
 #pragma unroll
         for (int n = 0; n < NT; ++n) {
-          *reinterpret_cast<float2*>(sh + gq * LDS_S + n * 8 + 2 * tq) = make_float2(sacc[n][0] * p.scale, sacc[n][1] * p.scale);
-          *reinterpret_cast<float2*>(sh + (gq + 8) * LDS_S + n * 8 + 2 * tq) = make_float2(sacc[n][2] * p.scale, sacc[n][3] * p.scale);
+          *reinterpret_cast<float2*>(sh + gq * LDS_S + n * 8 + 2 * tq) = make_float2(sacc[n][0], sacc[n][1]);
+          *reinterpret_cast<float2*>(sh + (gq + 8) * LDS_S + n * 8 + 2 * tq) = make_float2(sacc[n][2], sacc[n][3]);
         }
       }
     }
@@ -126,7 +131,7 @@ __global__ void __launch_bounds__(NW * 32, MINB) attn_talk_tc_kernel(const pcs_a
     for (int g2 = 0; g2 < H; ++g2) {
       float w[HPW];
 #pragma unroll
-      for (int i = 0; i < HPW; ++i) w[i] = warp * HPW + i < H ? Tk[(warp * HPW + i) * H + g2] : 0.f;
+      for (int i = 0; i < HPW; ++i) w[i] = Tw[i * H + g2];
       const float* sg = Ss + static_cast<long long>(g2) * TT_BM * LDS_S;
 #pragma unroll
       for (int n = 0; n < NT; ++n) {
@@ -150,17 +155,25 @@ __global__ void __launch_bounds__(NW * 32, MINB) attn_talk_tc_kernel(const pcs_a
       if (h < H) {
         float (&s)[NT][4] = sm_[i];
         float mx_a = -INFINITY, mx_b = -INFINITY;
+        if (full_tile) {   // every key of the tile is seen by every row of the block: no mask
 #pragma unroll
-        for (int n = 0; n < NT; ++n) {
+          for (int n = 0; n < NT; ++n) {
+            mx_a = fmaxf(mx_a, fmaxf(s[n][0], s[n][1]));
+            mx_b = fmaxf(mx_b, fmaxf(s[n][2], s[n][3]));
+          }
+        } else {
 #pragma unroll
-          for (int c = 0; c < 2; ++c) {
-            const int j = j0 + n * 8 + 2 * tq + c;
-            const bool ok_a = j <= pos_a && (p.window <= 0 || pos_a - j < p.window);
-            const bool ok_b = j <= pos_b && (p.window <= 0 || pos_b - j < p.window);
-            if (!ok_a) s[n][c] = -INFINITY;
-            if (!ok_b) s[n][2 + c] = -INFINITY;
-            mx_a = fmaxf(mx_a, s[n][c]);
-            mx_b = fmaxf(mx_b, s[n][2 + c]);
+          for (int n = 0; n < NT; ++n) {
+#pragma unroll
+            for (int c = 0; c < 2; ++c) {
+              const int j = j0 + n * 8 + 2 * tq + c;
+              const bool ok_a = j <= pos_a && (p.window <= 0 || pos_a - j < p.window);
+              const bool ok_b = j <= pos_b && (p.window <= 0 || pos_b - j < p.window);
+              if (!ok_a) s[n][c] = -INFINITY;
+              if (!ok_b) s[n][2 + c] = -INFINITY;
+              mx_a = fmaxf(mx_a, s[n][c]);
+              mx_b = fmaxf(mx_b, s[n][2 + c]);
+            }
           }
         }
         mx_a = fmaxf(mx_a, __shfl_xor_sync(0xffffffffu, mx_a, 1));
@@ -169,14 +182,17 @@ __global__ void __launch_bounds__(NW * 32, MINB) attn_talk_tc_kernel(const pcs_a
         mx_b = fmaxf(mx_b, __shfl_xor_sync(0xffffffffu, mx_b, 2));
         const float mn_a = fmaxf(mrow[i][0], mx_a), mn_b = fmaxf(mrow[i][1], mx_b);
         const float use_a = mn_a == -INFINITY ? 0.f : mn_a, use_b = mn_b == -INFINITY ? 0.f : mn_b;   // a row that has seen no key yet
-        const float f_a = mrow[i][0] == -INFINITY ? 0.f : expf(mrow[i][0] - use_a), f_b = mrow[i][1] == -INFINITY ? 0.f : expf(mrow[i][1] - use_b);
+        // exponentials through the base-2 unit (relative error 2^-22, far below the operands' rounding): exp(x) = 2^(x log2 e)
+        constexpr float kLog2e = 1.4426950408889634f;
+        const float ua = use_a * kLog2e, ub = use_b * kLog2e;
+        const float f_a = mrow[i][0] == -INFINITY ? 0.f : ex2(mrow[i][0] * kLog2e - ua), f_b = mrow[i][1] == -INFINITY ? 0.f : ex2(mrow[i][1] * kLog2e - ub);
         float sum_a = 0.f, sum_b = 0.f;
 #pragma unroll
         for (int n = 0; n < NT; ++n) {
-          s[n][0] = expf(s[n][0] - use_a);
-          s[n][1] = expf(s[n][1] - use_a);
-          s[n][2] = expf(s[n][2] - use_b);
-          s[n][3] = expf(s[n][3] - use_b);
+          s[n][0] = ex2(fmaf(s[n][0], kLog2e, -ua));
+          s[n][1] = ex2(fmaf(s[n][1], kLog2e, -ua));
+          s[n][2] = ex2(fmaf(s[n][2], kLog2e, -ub));
+          s[n][3] = ex2(fmaf(s[n][3], kLog2e, -ub));
           sum_a += s[n][0] + s[n][1];
           sum_b += s[n][2] + s[n][3];
         }
@@ -188,12 +204,14 @@ __global__ void __launch_bounds__(NW * 32, MINB) attn_talk_tc_kernel(const pcs_a
         mrow[i][1] = mn_b;
         lrow[i][0] = lrow[i][0] * f_a + sum_a;
         lrow[i][1] = lrow[i][1] * f_b + sum_b;
+        if (__any_sync(0xffffffffu, f_a != 1.f || f_b != 1.f)) {   // (after the first tiles the maxima rarely move)
 #pragma unroll
-        for (int n = 0; n < WP / 8; ++n) {
-          oacc[i][n][0] *= f_a;
-          oacc[i][n][1] *= f_a;
-          oacc[i][n][2] *= f_b;
-          oacc[i][n][3] *= f_b;
+          for (int n = 0; n < WP / 8; ++n) {
+            oacc[i][n][0] *= f_a;
+            oacc[i][n][1] *= f_a;
+            oacc[i][n][2] *= f_b;
+            oacc[i][n][3] *= f_b;
+          }
         }
         const __nv_bfloat16* vh = Vs + static_cast<long long>(h / rep) * BN * LD;
 #pragma unroll
@@ -268,7 +286,7 @@ int launch_one(const pcs_attn_params& p, cudaStream_t st, size_t smem) {
 
 size_t talk_tc_smem(int H, int G, int WP, int BN) {
   const size_t LD = WP + TT_PAD;
-  return (static_cast<size_t>(H) * TT_BM + 2 * static_cast<size_t>(G) * BN) * LD * 2 + static_cast<size_t>(H) * TT_BM * (BN + 8) * 4 + static_cast<size_t>(H) * H * 4;
+  return (static_cast<size_t>(H) * TT_BM + 2 * static_cast<size_t>(G) * BN) * LD * 2 + static_cast<size_t>(H) * TT_BM * (BN + 8) * 4 + static_cast<size_t>(16) * H * 4;
 }
 
 }  // namespace
