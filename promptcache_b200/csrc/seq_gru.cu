@@ -3,105 +3,107 @@
 // where pz, u and g are projections of the layer's input (biases already added).  Because neither z nor c depends on the state,
 // every step is an affine map S -> a S + b with a = 1 - z, b = z c, and maps compose: a stretch of tokens is one pair (A, B).
 //
-// One block = 16 neighbouring channels of one batch entry x up to 64 segments of the entry's tokens (16 x segments threads;
-// the launch picks the number of segments from the longest entry, so that a segment holds at least 16 tokens).
-//   pass 1   every thread folds its segment into (A, B), starting from the identity;
-//   join     the segments' pairs meet in shared memory; a thread's true start state is the entry's state (the slot pool's, or
-//            zero for an entry whose slot holds no tokens) carried through the segments before its own, in order;
-//   pass 2   the segment is walked again from that state and the gated result is written (its inputs come from L1 / L2).
-// Both passes take eight tokens at a time: their loads are issued together, then the eight dependent updates follow.  The first
-// segment's threads carry the state through all segments and store it for the next step.  A decoding step is the case of one
-// token and one segment.  State, gates and candidates are 32-bit in both types; a channel's loads of neighbouring threads are
-// neighbouring elements.
+// One block = a few neighbouring channels of one batch entry x up to 64 segments of the entry's tokens; a thread owns one channel
+// of one segment, at most 32 tokens at a time (a longer entry is walked in stretches of segments x 32 tokens, the state carried
+// from stretch to stretch).
+//   fold     a thread reads its tokens' gate and candidate inputs ONCE (sixteen tokens' loads are issued together) and keeps, for
+//            every token i of its segment, the composed map of the segment up to and including i, (A_i, B_i), in registers;
+//   join     the segments' whole maps meet in shared memory; every thread carries the state at the stretch's start through the
+//            segments in order, notes the state at its own segment's start, and ends with the state after the stretch;
+//   write    S_i = A_i S_start + B_i for every token: no chain is left, only the gate input is read.
+// A prompt of 2048 tokens is 32 dependent steps and one read of its inputs.  A decoding step is the case of one token and one
+// segment.  State, gates and candidates are 32-bit in both types; neighbouring threads load neighbouring elements.
+#include <type_traits>
+
 #include "seq_common.cuh"
 
 namespace pcs {
 
-constexpr int kGruMaxSegs = 64, kGruChannels = 16, kGruUnroll = 8;
+constexpr int kGruMaxSegs = 64, kGruPer = 32, kGruUnroll = 16, kGruThreads = 512, kGruSMs = 148;
 
+// float32 runs take the library's exponential and a true division; bfloat16 runs the hardware's base-2 exponential and
+// reciprocal (a relative error near 2^-22, in 32-bit all the same): the scan is bound by instruction issue, not by bytes
+template <bool kFast>
+__device__ __forceinline__ float gru_sigmoid(float z) {
+  if constexpr (kFast) return __fdividef(1.f, 1.f + __expf(-z));
+  else return sigmoidf_(z);
+}
+
+template <bool kFast>
 __device__ __forceinline__ void gru_step(float pz, float u, float& a, float& b) {
-  const float z = sigmoidf_(pz);
-  const float c = u >= 0.f ? u + 0.5f : sigmoidf_(u);
+  const float z = gru_sigmoid<kFast>(pz);
+  const float c = u >= 0.f ? u + 0.5f : gru_sigmoid<kFast>(u);
   a = 1.f - z;
   b = z * c;
 }
 
 template <typename T>
-__global__ void __launch_bounds__(kGruChannels * kGruMaxSegs) gru_scan_kernel(const pcs_gru_params p) {
-  __shared__ float As[kGruMaxSegs][kGruChannels], Bs[kGruMaxSegs][kGruChannels];
-  const int lane = threadIdx.x, seg = threadIdx.y, n_segs = blockDim.y, b = blockIdx.y;
-  const int c = blockIdx.x * kGruChannels + lane;
+__global__ void __launch_bounds__(kGruThreads) gru_scan_kernel(const pcs_gru_params p) {
+  __shared__ float As[kGruThreads], Bs[kGruThreads];
+  constexpr bool kFast = !std::is_same<T, float>::value;
+  const int lane = threadIdx.x, ch = blockDim.x, seg = threadIdx.y, n_segs = blockDim.y, b = blockIdx.y;
+  const int c = blockIdx.x * ch + lane;
   const int len = p.seq_len[b], off = p.seq_off[b], pos0 = p.seq_pos0[b], slot = p.seq_slot[b];
-  const int per = (len + n_segs - 1) / n_segs;
-  const int t0 = min(len, seg * per), t1 = min(len, t0 + per);
+  int per = (len + n_segs - 1) / n_segs;   // tokens of a segment in one stretch; stretches of equal size
+  if (per > kGruPer) per = (per + (per + kGruPer - 1) / kGruPer - 1) / ((per + kGruPer - 1) / kGruPer);
+  const int stretch = per * n_segs;
   const bool live = c < p.width;
   const long long rs = p.row_stride;
   const T* base = static_cast<const T*>(p.proj) + static_cast<long long>(off) * rs + (live ? c : 0);
-  float A = 1.f, B = 0.f;
-  if (live && n_segs > 1) {   // (one segment: nothing to fold ahead of pass 2)
-    int t = t0;
-    for (; t + kGruUnroll <= t1; t += kGruUnroll) {
-      float pz[kGruUnroll], u[kGruUnroll];
+  T* out = static_cast<T*>(p.out) + static_cast<long long>(off) * p.width + (live ? c : 0);
+  float* state = p.s_pool + static_cast<long long>(slot) * p.width + (live ? c : 0);
+  float S = (live && pos0 > 0) ? *state : 0.f;   // the state at the start of the stretch
+  for (int s0 = 0; s0 < len; s0 += stretch) {
+    const int t0 = min(len, s0 + seg * per), n = min(len, t0 + per) - t0;
+    float Ap[kGruPer], Bp[kGruPer];
+    float A = 1.f, B = 0.f;
 #pragma unroll
-      for (int i = 0; i < kGruUnroll; ++i) {
-        const T* row = base + static_cast<long long>(t + i) * rs;
-        pz[i] = ldf(row + p.z_off);
-        u[i] = ldf(row + p.x_off);
+    for (int j = 0; j < kGruPer; j += kGruUnroll) {
+      if (j < n) {
+        float pz[kGruUnroll], u[kGruUnroll];
+#pragma unroll
+        for (int i = 0; i < kGruUnroll; ++i) {
+          const T* row = base + static_cast<long long>(t0 + min(j + i, n - 1)) * rs;
+          pz[i] = ldf(row + p.z_off);
+          u[i] = ldf(row + p.x_off);
+        }
+#pragma unroll
+        for (int i = 0; i < kGruUnroll; ++i) {
+          if (j + i < n) {
+            float a, bb;
+            gru_step<kFast>(pz[i], u[i], a, bb);
+            A *= a;
+            B = fmaf(a, B, bb);
+            Ap[j + i] = A;
+            Bp[j + i] = B;
+          }
+        }
       }
+    }
+    As[seg * ch + lane] = A;
+    Bs[seg * ch + lane] = B;
+    __syncthreads();
+    float mine = S;
+    for (int s = 0; s < n_segs; ++s) {
+      if (s == seg) mine = S;
+      S = fmaf(As[s * ch + lane], S, Bs[s * ch + lane]);
+    }
+    if (live) {
 #pragma unroll
-      for (int i = 0; i < kGruUnroll; ++i) {
-        float a, bb;
-        gru_step(pz[i], u[i], a, bb);
-        A *= a;
-        B = fmaf(a, B, bb);
+      for (int j = 0; j < kGruPer; j += kGruUnroll) {
+        if (j < n) {
+          float g[kGruUnroll];
+#pragma unroll
+          for (int i = 0; i < kGruUnroll; ++i) g[i] = ldf(base + static_cast<long long>(t0 + min(j + i, n - 1)) * rs + p.g_off);
+#pragma unroll
+          for (int i = 0; i < kGruUnroll; ++i)
+            if (j + i < n) stf(out + static_cast<long long>(t0 + j + i) * p.width, fmaf(Ap[j + i], mine, Bp[j + i]) * (g[i] * gru_sigmoid<kFast>(g[i])));
+        }
       }
     }
-    for (; t < t1; ++t) {
-      const T* row = base + static_cast<long long>(t) * rs;
-      float a, bb;
-      gru_step(ldf(row + p.z_off), ldf(row + p.x_off), a, bb);
-      A *= a;
-      B = fmaf(a, B, bb);
-    }
+    __syncthreads();   // the next stretch overwrites the segments' maps
   }
-  As[seg][lane] = A;
-  Bs[seg][lane] = B;
-  __syncthreads();
-  if (!live) return;
-  float* state = p.s_pool + static_cast<long long>(slot) * p.width + c;
-  float S = pos0 > 0 ? *state : 0.f;
-  for (int s = 0; s < seg; ++s) S = fmaf(As[s][lane], S, Bs[s][lane]);
-  T* out = static_cast<T*>(p.out) + static_cast<long long>(off) * p.width + c;
-  int t = t0;
-  for (; t + kGruUnroll <= t1; t += kGruUnroll) {
-    float pz[kGruUnroll], u[kGruUnroll], g[kGruUnroll];
-#pragma unroll
-    for (int i = 0; i < kGruUnroll; ++i) {
-      const T* row = base + static_cast<long long>(t + i) * rs;
-      pz[i] = ldf(row + p.z_off);
-      u[i] = ldf(row + p.x_off);
-      g[i] = ldf(row + p.g_off);
-    }
-#pragma unroll
-    for (int i = 0; i < kGruUnroll; ++i) {
-      float a, bb;
-      gru_step(pz[i], u[i], a, bb);
-      S = fmaf(a, S, bb);
-      stf(out + static_cast<long long>(t + i) * p.width, S * (g[i] * sigmoidf_(g[i])));
-    }
-  }
-  for (; t < t1; ++t) {
-    const T* row = base + static_cast<long long>(t) * rs;
-    float a, bb;
-    gru_step(ldf(row + p.z_off), ldf(row + p.x_off), a, bb);
-    S = fmaf(a, S, bb);
-    const float g = ldf(row + p.g_off);
-    stf(out + static_cast<long long>(t) * p.width, S * (g * sigmoidf_(g)));
-  }
-  if (seg == 0) {   // the state after the entry's last token: through the other segments' pairs
-    for (int s = 1; s < n_segs; ++s) S = fmaf(As[s][lane], S, Bs[s][lane]);
-    *state = S;
-  }
+  if (live && seg == 0 && len > 0) *state = S;
 }
 
 }  // namespace pcs
@@ -114,7 +116,22 @@ PCS_API int pcs_gru_scan(const pcs_gru_params* p, void* stream) {
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   int segs = 1;   // a segment holds at least 16 tokens of the longest entry
   while (segs < pcs::kGruMaxSegs && p->max_len >= 32 * segs) segs *= 2;
-  dim3 grid((p->width + pcs::kGruChannels - 1) / pcs::kGruChannels, p->n_seqs), block(pcs::kGruChannels, segs);
+  int ch = pcs::kGruThreads / segs;   // channels of a block: a warp's worth for short steps
+  if (ch > 32) ch = 32;
+  if (segs == pcs::kGruMaxSegs) {
+    // long prompts: the launch is bound by instruction issue, so what counts is how evenly the blocks (one resident per SM) fill
+    // the SMs: the channel count with the fewest rounds of blocks x channels per block; more channels mean fewer segments and
+    // more stretches, which costs little beside that
+    long long best = -1;
+    for (int c = 6; c <= 32; ++c) {
+      const long long blocks = static_cast<long long>((p->width + c - 1) / c) * p->n_seqs;
+      const long long cost = ((blocks + pcs::kGruSMs - 1) / pcs::kGruSMs) * c;
+      if (best < 0 || cost <= best) { best = cost; ch = c; }
+    }
+    segs = pcs::kGruThreads / ch;
+    if (segs > pcs::kGruMaxSegs) segs = pcs::kGruMaxSegs;
+  }
+  dim3 grid((p->width + ch - 1) / ch, p->n_seqs), block(ch, segs);
   PCS_DISPATCH(p->dtype, pcs::gru_scan_kernel<T><<<grid, block, 0, st>>>(*p));
   PCS_CHECK_CUDA(cudaGetLastError());
   pcs::count_launch();
