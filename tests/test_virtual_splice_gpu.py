@@ -202,7 +202,7 @@ def test_generation_through_the_virtual_splice_equals_the_copied_path(native):
 
 
 def test_gqa_engine_cache_shape_and_virtual_splice(native):
-    """Hkv < H through the engine (ADVICE: get_cache_shape must size the prompt cache for the KV heads)."""
+    """Hkv < H through the engine (get_cache_shape must size the prompt cache for the KV heads)."""
     eng, lm, case, prompt = _engine(heads=8, kv_heads=2, hidden=1024, seg_lens=(130, 24, 260), suffix=4, max_ctx=640)
     assert lm.get_cache_shape() == (2, 2, 128) and eng.prompt_cache.buffer.shape[2] == 2
     text_v = _greedy(lm, eng, prompt, n=4)
